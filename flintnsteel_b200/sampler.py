@@ -1,0 +1,248 @@
+"""ctypes binding of the C ABI in ``include/fns_b200.h`` for tests, the benchmark and the multi-GPU dispatcher.
+
+The CUDA library is the only implementation: if it is missing the import of this module's ``load_library``
+fails loudly; there is no CPU path.  torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+OK, ERR_ARG, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE = 0, 1, 2, 3, 4
+F32, BF16 = 0, 1
+EMPTY_ID = 0x7FFFFFFF
+MAX_K = 1024
+
+#: ``fns_b200_params`` (48 bytes); the reference's ``fns::SampleParams`` (include/fns/engine.h:75-84) plus the
+#: Philox counter and the three extension terms.
+PARAMS_DTYPE = np.dtype(
+    [
+        ("temperature", "<f4"),
+        ("top_p", "<f4"),
+        ("min_p", "<f4"),
+        ("repetition", "<f4"),
+        ("presence", "<f4"),
+        ("frequency", "<f4"),
+        ("top_k", "<i4"),
+        ("reserved", "<i4"),
+        ("seed", "<u8"),
+        ("counter", "<u8"),
+    ],
+    align=True,
+)
+assert PARAMS_DTYPE.itemsize == 48
+
+#: ``fns_b200_cand``: (value, id), the pair the reference keeps in g_cand_v / g_cand_i (src/kernels.cu:601-602).
+CAND_DTYPE = np.dtype([("value", "<f4"), ("id", "<i4")])
+
+#: every symbol that ``include/fns_b200.h`` declares
+SYMBOLS = [
+    "fns_b200_create",
+    "fns_b200_destroy",
+    "fns_b200_last_error",
+    "fns_b200_device_status",
+    "fns_b200_k_cap",
+    "fns_b200_sample_rows",
+    "fns_b200_sample_one",
+    "fns_b200_select_rows",
+    "fns_b200_finalize_rows",
+    "fns_b200_verify_accept",
+    "fns_b200_presence_apply",
+    "fns_b200_presence_mark",
+    "fns_b200_presence_apply_col",
+    "fns_b200_presence_mark_n",
+    "fns_b200_io_advance",
+    "fns_b200_plan",
+    "fns_b200_set_slices",
+]
+
+_lib = None
+
+
+class SamplerError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"fns_b200 status {code}: {text}")
+        self.code = code
+
+
+def make_params(rows: int, **fields) -> np.ndarray:
+    """Host array of ``rows`` parameter structs with the reference's defaults (greedy, top_p 1, k_cap)."""
+    p = np.zeros(rows, dtype=PARAMS_DTYPE)
+    p["top_p"] = 1.0
+    p["repetition"] = 1.0
+    for name, value in fields.items():
+        p[name] = value
+    return p
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads ``lib/libfns_b200.so``.  Raises if it has not been built: nothing stands in for it."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m flintnsteel_b200.build` (there is no CPU fallback)"
+        )
+    lib = ctypes.CDLL(path)
+    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+    lib.fns_b200_create.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(vp)]
+    lib.fns_b200_destroy.argtypes = [vp]
+    lib.fns_b200_last_error.argtypes = [vp]
+    lib.fns_b200_last_error.restype = ctypes.c_char_p
+    lib.fns_b200_device_status.argtypes = [vp, vp]
+    lib.fns_b200_k_cap.argtypes = [vp]
+    lib.fns_b200_sample_rows.argtypes = [vp, vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
+    lib.fns_b200_sample_one.argtypes = [vp, vp, i32, i32, vp, vp, i32, vp, vp, vp]
+    lib.fns_b200_select_rows.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
+    lib.fns_b200_finalize_rows.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp]
+    lib.fns_b200_verify_accept.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, vp, i64, vp, i64, vp, vp, vp, vp, vp]
+    lib.fns_b200_presence_apply.argtypes = [vp, vp, i32, f32, vp]
+    lib.fns_b200_presence_mark.argtypes = [vp, vp, vp]
+    lib.fns_b200_presence_apply_col.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    lib.fns_b200_presence_mark_n.argtypes = [vp, vp, i32, vp]
+    lib.fns_b200_io_advance.argtypes = [vp, i32, vp]
+    lib.fns_b200_plan.argtypes = [vp, i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.fns_b200_set_slices.argtypes = [vp, i32]
+    for name in SYMBOLS:
+        if name != "fns_b200_last_error":
+            getattr(lib, name).restype = i32
+    _lib = lib
+    return lib
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _dtype_code(t) -> int:
+    import torch
+
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"logits must be float32 or bfloat16, got {t.dtype}")
+
+
+def _stream():
+    import torch
+
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def params_to_device(params: np.ndarray, device):
+    """Uploads a host parameter array as a uint8 tensor of the same bytes."""
+    import torch
+
+    assert params.dtype == PARAMS_DTYPE
+    return torch.from_numpy(params.view(np.uint8).reshape(-1).copy()).to(device)
+
+
+class Sampler:
+    """One workspace (``fns_b200_sampler``) on one GPU.  Arguments are CUDA tensors; calls are asynchronous on
+    torch's current stream, like the C calls they forward to."""
+
+    def __init__(self, device: int = 0, max_rows: int = 256, max_vocab: int = 151936, k_cap: int = 64,
+                 max_history: int = 4096):
+        self.lib = load_library()
+        self.device = int(device)
+        self.k_cap = int(k_cap)
+        h = ctypes.c_void_p()
+        rc = self.lib.fns_b200_create(self.device, max_rows, max_vocab, k_cap, max_history, ctypes.byref(h))
+        if rc != OK:
+            raise SamplerError(rc, "fns_b200_create failed")
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.fns_b200_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != OK:
+            raise SamplerError(rc, self.lib.fns_b200_last_error(self.handle).decode())
+
+    def set_slices(self, slices: int):
+        self._check(self.lib.fns_b200_set_slices(self.handle, slices))
+
+    def plan(self, dtype: int, vocab: int, rows: int, history_bound: int = 0):
+        s, l, b = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        self._check(self.lib.fns_b200_plan(self.handle, dtype, vocab, rows, history_bound, ctypes.byref(s),
+                                           ctypes.byref(l), ctypes.byref(b)))
+        return {"slices": s.value, "slice_len": l.value, "smem_bytes": b.value}
+
+    def device_status(self):
+        self._check(self.lib.fns_b200_device_status(self.handle, _stream()))
+
+    def sample_rows(self, logits, params, out, masks=None, history=None, history_len=None, vocab=None):
+        rows = logits.shape[0]
+        vocab = int(vocab if vocab is not None else logits.shape[1])
+        self._check(self.lib.fns_b200_sample_rows(
+            self.handle, _ptr(logits), _dtype_code(logits), logits.stride(0), vocab, rows,
+            _ptr(masks), masks.stride(0) if masks is not None else 0,
+            _ptr(history), history.stride(0) if history is not None else 0, _ptr(history_len),
+            _ptr(params), _ptr(out), _stream()))
+        return out
+
+    def sample_one(self, logits, params_host: np.ndarray, out, mask=None):
+        p = np.ascontiguousarray(params_host.reshape(-1)[:1])
+        self._check(self.lib.fns_b200_sample_one(
+            self.handle, _ptr(logits), _dtype_code(logits), logits.numel(), _ptr(mask), None, 0,
+            ctypes.c_void_p(p.ctypes.data), _ptr(out), _stream()))
+        return out
+
+    def select_rows(self, logits, params, out_cands, id_base=0, masks=None, history=None, history_len=None,
+                    vocab=None):
+        rows = logits.shape[0]
+        vocab = int(vocab if vocab is not None else logits.shape[1])
+        self._check(self.lib.fns_b200_select_rows(
+            self.handle, _ptr(logits), _dtype_code(logits), logits.stride(0), vocab, rows, int(id_base),
+            _ptr(masks), masks.stride(0) if masks is not None else 0,
+            _ptr(history), history.stride(0) if history is not None else 0, _ptr(history_len),
+            _ptr(params), _ptr(out_cands), _stream()))
+        return out_cands
+
+    def finalize_rows(self, cands, lists: int, list_len: int, rows: int, params, out_tokens=None, out_cands=None):
+        self._check(self.lib.fns_b200_finalize_rows(
+            self.handle, _ptr(cands), lists, list_len, rows, _ptr(params), _ptr(out_tokens), _ptr(out_cands),
+            _stream()))
+
+    def verify_accept(self, logits, draft, params, out_tokens, out_accept, masks=None, history=None,
+                      history_len=None, vocab=None):
+        n_draft = int(draft.shape[1])
+        windows = int(draft.shape[0])
+        assert logits.shape[0] == windows * (n_draft + 1)
+        vocab = int(vocab if vocab is not None else logits.shape[1])
+        self._check(self.lib.fns_b200_verify_accept(
+            self.handle, _ptr(logits), _dtype_code(logits), logits.stride(0), vocab, windows, n_draft, _ptr(draft),
+            _ptr(masks), masks.stride(0) if masks is not None else 0,
+            _ptr(history), history.stride(0) if history is not None else 0, _ptr(history_len),
+            _ptr(params), _ptr(out_tokens), _ptr(out_accept), _stream()))
+
+
+def cands_tensor(rows: int, k_cap: int, device):
+    """Device buffer for ``rows * k_cap`` ``fns_b200_cand`` entries (as int32 pairs: value bits, id)."""
+    import torch
+
+    return torch.empty((rows, k_cap, 2), dtype=torch.int32, device=device)
+
+
+def cands_to_numpy(t) -> np.ndarray:
+    """(rows, k_cap) structured array with fields value / id from a ``cands_tensor``."""
+    a = t.detach().cpu().numpy()
+    out = np.empty(a.shape[:2], dtype=CAND_DTYPE)
+    out["value"] = a[..., 0].view(np.float32)
+    out["id"] = a[..., 1]
+    return out

@@ -1,0 +1,164 @@
+/* fns_b200.h - C ABI of the B200 (sm_100a) token sampler: logits -> token for one decoding step.
+ *
+ * Plain C: pointers and sizes only.  Unless a name ends in `_host`, every data pointer is DEVICE memory owned
+ * by the caller; every call is asynchronous on the caller's stream (a cudaStream_t passed as void *; NULL is
+ * the default stream) and performs no host synchronisation and no allocation.  The library owns only the
+ * workspace created by fns_b200_create.  Every function returns a status (0 = FNS_B200_OK) and never aborts.
+ *
+ * Each entry point names the interface of the reference (NomenAK/FlintNSteel) that it replaces.
+ */
+#ifndef FNS_B200_H
+#define FNS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    FNS_B200_OK = 0,
+    FNS_B200_ERR_ARG = 1,      /* null pointer, size out of range, misuse */
+    FNS_B200_ERR_CUDA = 2,     /* a CUDA call failed; see fns_b200_last_error */
+    FNS_B200_ERR_CAPACITY = 3, /* rows / vocab / history beyond what the handle was created for */
+    FNS_B200_ERR_DEVICE = 4    /* a kernel recorded an internal error (fns_b200_device_status) */
+};
+
+enum { FNS_B200_F32 = 0, FNS_B200_BF16 = 1 };
+
+/* Empty candidate slot, as the reference's (-FLT_MAX, 0x7fffffff) (src/kernels.cu:632-633). */
+#define FNS_B200_EMPTY_ID 0x7fffffff
+/* Largest k_cap a handle accepts.  k_cap = 64 is the reference's kSampleMaxK (src/kernels.cu:598). */
+#define FNS_B200_MAX_K 1024
+#define FNS_B200_MAX_HISTORY 65000
+/* Verification window width limit; the reference's engine uses at most 8 columns (src/engine.cu:74,718). */
+#define FNS_B200_MAX_WINDOW 32
+
+/* Per-row sampling parameters; an array of these lives in device memory.
+ * Extends fns::SampleParams (include/fns/engine.h:75-84: temperature, top_p, top_k, seed, presence_penalty)
+ * with the Philox counter that Engine::pick_async takes beside it (src/engine.cu:823) and with min_p,
+ * repetition and frequency, which the reference does not have (neutral values: 0, 1, 0).
+ *   temperature <= 0 : greedy, first candidate in the total order (src/kernels.cu:701)
+ *   top_k <= 0 or > k_cap : k_cap candidates (src/kernels.cu:778)
+ *   top_p : cut on the temperature-1 softmax over the k candidates (src/kernels.cu:702-710)
+ *   min_p : after the top-p cut, keep the longest prefix with exp(v_j - v_0) >= min_p
+ *   penalties, for an id that occurs c > 0 times in the row's history, fp32, each step rounded:
+ *       x = x > 0 ? x / repetition : x * repetition;  x -= frequency * c;  x -= presence
+ *     (with repetition 1 and frequency 0: the reference's x - presence * seen, src/kernels.cu:726) */
+typedef struct fns_b200_params {
+    float temperature;
+    float top_p;
+    float min_p;
+    float repetition;
+    float presence;
+    float frequency;
+    int32_t top_k;
+    int32_t reserved;
+    uint64_t seed;
+    uint64_t counter;
+} fns_b200_params;
+
+/* One top-k candidate: penalised logit and GLOBAL token id.  Lists are sorted in the reference's total order
+ * (value descending, then id ascending, src/kernels.cu:594) and padded with (-FLT_MAX, FNS_B200_EMPTY_ID).
+ * This is the (value, id) pair the reference keeps in g_cand_v / g_cand_i (src/kernels.cu:601-602) and the
+ * unit that vocabulary shards exchange. */
+typedef struct fns_b200_cand {
+    float value;
+    int32_t id;
+} fns_b200_cand;
+
+typedef struct fns_b200_sampler fns_b200_sampler;
+
+/* Workspace for up to max_rows rows of up to max_vocab logits per call, k_cap in [1, FNS_B200_MAX_K], histories
+ * of up to max_history ids per row.  Replaces the reference's file-scope candidate arrays
+ * (src/kernels.cu:601-602), which make its sampler one-row-at-a-time; a handle serves one stream at a time,
+ * separate handles run concurrently.  Allocates device memory on `device` (the only allocating call besides
+ * the lazy default handle of the fns::k compatibility layer). */
+int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_history, fns_b200_sampler ** out);
+int fns_b200_destroy(fns_b200_sampler * s);
+/* Text of the last failure on this handle (host string, valid until the next call on the handle). */
+const char * fns_b200_last_error(const fns_b200_sampler * s);
+/* Synchronises the stream and returns FNS_B200_ERR_DEVICE if a kernel of this handle recorded an internal
+ * error since the last call (candidate buffer or history table overflow; neither can happen within the
+ * limits checked at launch).  For tests; the sampling calls themselves never synchronise. */
+int fns_b200_device_status(fns_b200_sampler * s, void * stream);
+int fns_b200_k_cap(const fns_b200_sampler * s);
+
+/* Rows of logits -> one token id per row.
+ * Replaces, for each row, the launch sequence of Engine::pick_async (src/engine.cu:837-843):
+ *   k::presence_apply (src/kernels.cuh:79)  +  k::argmax (:69) or k::sample (:74-75)
+ * in one fused pass that leaves the logits untouched.
+ *   logits       [rows][row_stride] elements of `dtype`; the first `vocab` of each row are used
+ *   masks        NULL, or [rows][mask_stride_words] packed uint32, token i <-> bit (i & 31) of word (i >> 5),
+ *                1 = allowed: the xgrammar bitmask as Engine::pick_async receives it
+ *                (include/fns/engine.h:115, src/kernels.cu:635)
+ *   history      NULL, or [rows][history_stride] token ids, of which history_len[r] are used for row r;
+ *                ids outside [0, vocab) are ignored (src/kernels.cu:730)
+ *   params       [rows]
+ *   out_tokens   [rows] int32; -1 when no allowed finite candidate exists (src/kernels.cu:700) */
+int fns_b200_sample_rows(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
+                         const uint32_t * masks, int64_t mask_stride_words, const int32_t * history,
+                         int64_t history_stride, const int32_t * history_len, const fns_b200_params * params,
+                         int32_t * out_tokens, void * stream);
+
+/* One row with parameters passed by value from the host: the shape of k::sample / k::argmax
+ * (src/kernels.cuh:69,74-75).  `params_host` is read during the call. */
+int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
+                        const int32_t * history, int history_len, const fns_b200_params * params_host,
+                        int32_t * out_token, void * stream);
+
+/* First half of the path only: per-row top-k candidates of a vocabulary SHARD, in the total order.
+ * The reference does the same per slice in k_topk_part (src/kernels.cu:624-648); here a shard is the slice
+ * that one GPU owns.  `id_base` is the global id of the shard's element 0: history ids are global, reported
+ * ids are global, `masks` points at the shard's own words (id_base must be a multiple of 32).
+ *   out_cands    [rows][k_cap]; entries beyond the row's k are empty */
+int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
+                         int32_t id_base, const uint32_t * masks, int64_t mask_stride_words,
+                         const int32_t * history, int64_t history_stride, const int32_t * history_len,
+                         const fns_b200_params * params, fns_b200_cand * out_cands, void * stream);
+
+/* Second half of the path: merge `lists` candidate lists per row (e.g. one per vocabulary shard, gathered into
+ * local memory) and draw.  This is k_sample (src/kernels.cu:671-721): selection rounds over the slices'
+ * candidates, then softmax / top-p / temperature / Philox draw.
+ *   cands        [rows][lists][list_len]; lists * list_len <= 8192
+ *   out_cands    NULL, or [rows][k_cap]: the merged list, for inspection */
+int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len, int rows,
+                           const fns_b200_params * params, int32_t * out_tokens, fns_b200_cand * out_cands,
+                           void * stream);
+
+/* Speculative verification of `windows` windows of W = n_draft + 1 logit rows each (row = window * W + c).
+ * Replaces the per-column loop of Engine::verify (src/engine.cu:750-757: k::presence_apply_col + k::argmax /
+ * k::sample with counter + c) and moves the host accept loop (tools/fns_serve/fns_serve.cpp:492-508) onto
+ * the device.  Column c is penalised with the window's history plus draft[0 .. c) (src/kernels.cu:738-741).
+ *   draft        [windows][n_draft] token ids proposed for columns 1 .. n_draft
+ *   params       [windows]; column c draws with params.counter + c
+ *   out_tokens   [windows][W]
+ *   out_accept   [windows]: a = number of leading c < n_draft with out_tokens[c] == draft[c]; the tokens to
+ *                emit are out_tokens[0 .. a] */
+int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab,
+                           int windows, int n_draft, const int32_t * draft, const uint32_t * masks,
+                           int64_t mask_stride_words, const int32_t * history, int64_t history_stride,
+                           const int32_t * history_len, const fns_b200_params * params, int32_t * out_tokens,
+                           int32_t * out_accept, void * stream);
+
+/* Dense presence state of the reference, kept for callers that drive it directly (src/kernels.cuh:77-88).
+ * Same arithmetic, same in-place update of the logits. */
+int fns_b200_presence_apply(float * x, const float * seen, int n, float penalty, void * stream);        /* :79 */
+int fns_b200_presence_mark(float * seen, const int32_t * token, void * stream);                         /* :80 */
+int fns_b200_presence_apply_col(float * x, const float * seen, const int32_t * draft, int c, int n,
+                                float penalty, void * stream);                                          /* :83-84 */
+int fns_b200_presence_mark_n(float * seen, const int32_t * tokens, int n, void * stream);               /* :85 */
+int fns_b200_io_advance(int32_t * io, int pos, void * stream);                                          /* :88 */
+
+/* Launch geometry chosen for a call (slices per row, threads, dynamic shared memory of the select kernel),
+ * for benchmarks and tests. */
+int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int history_bound, int * slices,
+                  int * slice_len, int * smem_bytes);
+/* Overrides the number of slices per row (0 = automatic).  For tests that must show that results do not depend
+ * on the launch geometry. */
+int fns_b200_set_slices(fns_b200_sampler * s, int slices);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FNS_B200_H */
