@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <vector>
 
 namespace fnsb {
 
@@ -470,8 +471,11 @@ struct fns_b200_sampler {
     int force_slices;
     uint64_t * cand;   // [max_rows][kMaxSlices or fewer][k_cap]
     size_t cand_entries;
-    int32_t * win_tokens;  // unused placeholder for future fused paths
     int * err;
+    int64_t launches;
+    bool prof_on;
+    int prof_calls;                   // calls recorded so far
+    std::vector<cudaEvent_t> prof_ev; // three per call: before select, after select, after finalize
     char msg[256];
 };
 
@@ -538,8 +542,14 @@ size_t final_smem(int lists, int list_len, int k_cap) {
 template <typename T, int VEC>
 cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
     auto kern = k_select<T, VEC, 2>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return e;
+    static bool configured[64] = {};  // per device: the opt-in to large dynamic shared memory is sticky
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
     kern<<<dim3((unsigned) a.slices, (unsigned) rows), kThreads, smem, st>>>(a);
     return cudaGetLastError();
 }
@@ -553,8 +563,14 @@ cudaError_t launch_select(const SelectArgs & a, int dtype, int vec, int rows, si
 
 cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
     const size_t smem = final_smem(a.lists, a.list_len, a.k_cap);
-    cudaError_t e = cudaFuncSetAttribute(k_finalize, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return e;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(k_finalize, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
     k_finalize<<<(unsigned) rows, kThreads, smem, st>>>(a);
     return cudaGetLastError();
 }
@@ -616,8 +632,12 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.ht_size = pl.ht_size;
     a.cand = s->cand;
     a.err = s->err;
+    const bool prof = s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size();
+    if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3], st);
     const cudaError_t e = launch_select(a, dtype, pl.vec, rows, pl.smem_select, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "select launch");
+    if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 1], st);
+    ++s->launches;
     return FNS_B200_OK;
 }
 
@@ -636,6 +656,11 @@ int run_final_internal(fns_b200_sampler * s, const Plan & pl, int rows, int n_dr
     f.out_cands = out_cands;
     const cudaError_t e = launch_final(f, rows, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "finalize launch");
+    ++s->launches;
+    if (s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size()) {
+        cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 2], st);
+        ++s->prof_calls;
+    }
     return FNS_B200_OK;
 }
 
@@ -659,6 +684,9 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
     s->k_cap = k_cap;
     s->max_history = max_history;
     s->force_slices = 0;
+    s->launches = 0;
+    s->prof_on = false;
+    s->prof_calls = 0;
     s->msg[0] = 0;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
@@ -690,7 +718,40 @@ int fns_b200_destroy(fns_b200_sampler * s) {
     DeviceGuard g(s->device);
     cudaFree(s->cand);
     cudaFree(s->err);
+    for (cudaEvent_t ev : s->prof_ev) cudaEventDestroy(ev);
     delete s;
+    return FNS_B200_OK;
+}
+
+int64_t fns_b200_launch_count(const fns_b200_sampler * s) { return s ? s->launches : 0; }
+
+int fns_b200_profile_begin(fns_b200_sampler * s, int max_calls) {
+    if (!s || max_calls <= 0 || max_calls > 100000) return FNS_B200_ERR_ARG;
+    DeviceGuard g(s->device);
+    while (s->prof_ev.size() < (size_t) max_calls * 3) {
+        cudaEvent_t ev;
+        if (cudaEventCreate(&ev) != cudaSuccess) return fail(s, FNS_B200_ERR_CUDA, "cudaEventCreate");
+        s->prof_ev.push_back(ev);
+    }
+    s->prof_calls = 0;
+    s->prof_on = true;
+    return FNS_B200_OK;
+}
+
+int fns_b200_profile_end(fns_b200_sampler * s, void * stream, double * select_ms, double * finalize_ms, int * calls) {
+    if (!s) return FNS_B200_ERR_ARG;
+    s->prof_on = false;
+    const cudaError_t e = cudaStreamSynchronize((cudaStream_t) stream);
+    if (e != cudaSuccess) return fail_cuda(s, e, "profile_end");
+    double a = 0.0, b = 0.0;
+    for (int i = 0; i < s->prof_calls; ++i) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, s->prof_ev[(size_t) i * 3], s->prof_ev[(size_t) i * 3 + 1]) == cudaSuccess) a += ms;
+        if (cudaEventElapsedTime(&ms, s->prof_ev[(size_t) i * 3 + 1], s->prof_ev[(size_t) i * 3 + 2]) == cudaSuccess) b += ms;
+    }
+    if (select_ms) *select_ms = a;
+    if (finalize_ms) *finalize_ms = b;
+    if (calls) *calls = s->prof_calls;
     return FNS_B200_OK;
 }
 
@@ -812,6 +873,7 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
                                                                                   out_accept);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(s, e, "accept launch");
+    ++s->launches;
     return FNS_B200_OK;
 }
 

@@ -58,6 +58,20 @@ SYMBOLS = [
     "fns_b200_io_advance",
     "fns_b200_plan",
     "fns_b200_set_slices",
+    "fns_b200_launch_count",
+    "fns_b200_profile_begin",
+    "fns_b200_profile_end",
+    "fns_b200_engine_create",
+    "fns_b200_engine_destroy",
+    "fns_b200_engine_last_error",
+    "fns_b200_engine_sampler",
+    "fns_b200_engine_pick_async",
+    "fns_b200_engine_pick_wait",
+    "fns_b200_engine_device_tokens",
+    "fns_b200_engine_reset",
+    "fns_b200_engine_append",
+    "fns_b200_engine_verify",
+    "fns_b200_lookup_draft",
 ]
 
 _lib = None
@@ -109,9 +123,28 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_io_advance.argtypes = [vp, i32, vp]
     lib.fns_b200_plan.argtypes = [vp, i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.fns_b200_set_slices.argtypes = [vp, i32]
+    f64p = ctypes.POINTER(ctypes.c_double)
+    lib.fns_b200_launch_count.argtypes = [vp]
+    lib.fns_b200_profile_begin.argtypes = [vp, i32]
+    lib.fns_b200_profile_end.argtypes = [vp, vp, f64p, f64p, ctypes.POINTER(i32)]
+    lib.fns_b200_engine_create.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(vp)]
+    lib.fns_b200_engine_destroy.argtypes = [vp]
+    lib.fns_b200_engine_last_error.argtypes = [vp]
+    lib.fns_b200_engine_sampler.argtypes = [vp]
+    lib.fns_b200_engine_pick_async.argtypes = [vp, vp, i32, i32, i64, i32, vp, vp, i64, vp, vp, vp]
+    lib.fns_b200_engine_pick_wait.argtypes = [vp, vp]
+    lib.fns_b200_engine_device_tokens.argtypes = [vp]
+    lib.fns_b200_engine_reset.argtypes = [vp, vp]
+    lib.fns_b200_engine_append.argtypes = [vp, vp, i64, i32, vp, vp]
+    lib.fns_b200_engine_verify.argtypes = [vp, vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp]
+    lib.fns_b200_lookup_draft.argtypes = [vp, i32, i32, vp]
     for name in SYMBOLS:
-        if name != "fns_b200_last_error":
-            getattr(lib, name).restype = i32
+        getattr(lib, name).restype = i32
+    lib.fns_b200_last_error.restype = ctypes.c_char_p
+    lib.fns_b200_engine_last_error.restype = ctypes.c_char_p
+    lib.fns_b200_launch_count.restype = ctypes.c_int64
+    lib.fns_b200_engine_sampler.restype = vp
+    lib.fns_b200_engine_device_tokens.restype = vp
     _lib = lib
     return lib
 
@@ -186,6 +219,19 @@ class Sampler:
     def device_status(self):
         self._check(self.lib.fns_b200_device_status(self.handle, _stream()))
 
+    def launch_count(self) -> int:
+        return int(self.lib.fns_b200_launch_count(self.handle))
+
+    def profile_begin(self, max_calls: int):
+        self._check(self.lib.fns_b200_profile_begin(self.handle, max_calls))
+
+    def profile_end(self):
+        """(select_ms, finalize_ms, calls) summed over the calls recorded since profile_begin."""
+        a, b, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_int()
+        self._check(self.lib.fns_b200_profile_end(self.handle, _stream(), ctypes.byref(a), ctypes.byref(b),
+                                                  ctypes.byref(n)))
+        return a.value, b.value, n.value
+
     def sample_rows(self, logits, params, out, masks=None, history=None, history_len=None, vocab=None):
         rows = logits.shape[0]
         vocab = int(vocab if vocab is not None else logits.shape[1])
@@ -246,3 +292,87 @@ def cands_to_numpy(t) -> np.ndarray:
     out["value"] = a[..., 0].view(np.float32)
     out["id"] = a[..., 1]
     return out
+
+
+def _host(a):
+    return None if a is None else ctypes.c_void_p(a.ctypes.data if isinstance(a, np.ndarray) else a.data_ptr())
+
+
+class Engine:
+    """``fns_b200_engine``: the sampler part of the reference's ``fns::Engine`` (pick_async / pick_wait / verify /
+    reset_presence / presence_commit, src/engine.cu:733-866) for a batch of sessions.  Host arguments are numpy
+    arrays or pinned CPU tensors; logits are a CUDA tensor, or a (pinned) CPU tensor with ``logits_on_host``."""
+
+    def __init__(self, device: int = 0, max_rows: int = 256, vocab: int = 151936, k_cap: int = 64,
+                 max_history: int = 4096):
+        self.lib = load_library()
+        self.vocab = vocab
+        h = ctypes.c_void_p()
+        rc = self.lib.fns_b200_engine_create(device, max_rows, vocab, k_cap, max_history, ctypes.byref(h))
+        if rc != OK:
+            raise SamplerError(rc, "fns_b200_engine_create failed")
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.fns_b200_engine_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != OK:
+            raise SamplerError(rc, self.lib.fns_b200_engine_last_error(self.handle).decode())
+
+    def launch_count(self) -> int:
+        return int(self.lib.fns_b200_launch_count(self.lib.fns_b200_engine_sampler(self.handle)))
+
+    def pick_async(self, logits, params_host, masks_host=None, history_host=None, history_len_host=None,
+                   logits_on_host=False):
+        rows = logits.shape[0]
+        hs = 0 if history_host is None else history_host.shape[1]
+        self._check(self.lib.fns_b200_engine_pick_async(
+            self.handle, ctypes.c_void_p(logits.data_ptr()), int(logits_on_host), _dtype_code(logits),
+            logits.stride(0), rows, _host(masks_host), _host(history_host), hs, _host(history_len_host),
+            _host(params_host), _stream()))
+
+    def pick_wait(self, rows: int) -> np.ndarray:
+        out = np.empty(rows, np.int32)
+        self._check(self.lib.fns_b200_engine_pick_wait(self.handle, _host(out)))
+        return out
+
+    def pick(self, logits, params_host, **kw) -> np.ndarray:
+        self.pick_async(logits, params_host, **kw)
+        return self.pick_wait(logits.shape[0])
+
+    def device_tokens_ptr(self) -> int:
+        return int(self.lib.fns_b200_engine_device_tokens(self.handle) or 0)
+
+    def reset(self):
+        self._check(self.lib.fns_b200_engine_reset(self.handle, _stream()))
+
+    def append(self, tokens_dev_ptr: int, tokens_stride: int, rows: int, counts_host=None):
+        self._check(self.lib.fns_b200_engine_append(self.handle, ctypes.c_void_p(tokens_dev_ptr), tokens_stride, rows,
+                                                    _host(counts_host), _stream()))
+
+    def verify(self, logits, draft_host: np.ndarray, params_host, masks_host=None):
+        windows, n_draft = draft_host.shape
+        tokens = np.empty((windows, n_draft + 1), np.int32)
+        accept = np.empty(windows, np.int32)
+        self._check(self.lib.fns_b200_engine_verify(
+            self.handle, ctypes.c_void_p(logits.data_ptr()), _dtype_code(logits), logits.stride(0), windows, n_draft,
+            _host(np.ascontiguousarray(draft_host, dtype=np.int32)), _host(masks_host), _host(params_host),
+            _host(tokens), _host(accept), _stream()))
+        return tokens, accept
+
+
+def lookup_draft(history, want: int) -> np.ndarray:
+    """Prompt-lookup draft of the reference (include/fns/lookup.h:12-27), through the library's host function."""
+    h = np.ascontiguousarray(history, dtype=np.int32)
+    out = np.zeros(max(want, 1), np.int32)
+    n = load_library().fns_b200_lookup_draft(_host(h), h.size, want, _host(out))
+    return out[:n].copy()

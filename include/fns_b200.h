@@ -150,6 +150,61 @@ int fns_b200_presence_apply_col(float * x, const float * seen, const int32_t * d
 int fns_b200_presence_mark_n(float * seen, const int32_t * tokens, int n, void * stream);               /* :85 */
 int fns_b200_io_advance(int32_t * io, int pos, void * stream);                                          /* :88 */
 
+/* Number of kernels this handle has launched since it was created (benchmarks report it). */
+int64_t fns_b200_launch_count(const fns_b200_sampler * s);
+/* Per-kernel device timing for benchmarks: between profile_begin and profile_end every sampling call on the
+ * handle brackets its select kernel and its finalize kernel with CUDA events recorded on the caller's stream
+ * (at most max_calls calls are recorded).  profile_end synchronises the stream and returns the summed
+ * durations in milliseconds and the number of calls recorded. */
+int fns_b200_profile_begin(fns_b200_sampler * s, int max_calls);
+int fns_b200_profile_end(fns_b200_sampler * s, void * stream, double * select_ms, double * finalize_ms, int * calls);
+
+/* ---- host-side glue: the sampler part of fns::Engine ---------------------------------------------------------
+ * The reference's Engine stages the host bitmask through pinned memory, launches the sampler after the forward
+ * pass on its stream, copies the 4-byte token back and records an event (Engine::pick_async / pick_wait,
+ * src/engine.cu:823-852); Engine::verify does the same for a window and synchronises (src/engine.cu:733-765).
+ * fns_b200_engine is that glue for `rows` independent sessions at once.  Pointers ending in _host are host
+ * memory (pageable is accepted; it is staged through the engine's pinned buffers, as src/engine.cu:833 does).
+ * Two picks may be in flight; pick_wait returns them in order. */
+typedef struct fns_b200_engine fns_b200_engine;
+
+int fns_b200_engine_create(int device, int max_rows, int vocab, int k_cap, int max_history, fns_b200_engine ** out);
+int fns_b200_engine_destroy(fns_b200_engine * e);
+const char * fns_b200_engine_last_error(const fns_b200_engine * e);
+fns_b200_sampler * fns_b200_engine_sampler(fns_b200_engine * e);
+
+/* Engine::pick_async (src/engine.cu:823-847).  logits: device [rows][row_stride], or host memory when
+ * logits_on_host != 0 (then they are copied to the device inside the call).  masks_host: NULL or
+ * [rows][ceil(vocab / 32)].  history_host: NULL to use the sessions' device-side histories (see
+ * fns_b200_engine_reset / append), else [rows][history_stride] with history_len_host[rows]. */
+int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int logits_on_host, int dtype,
+                               int64_t row_stride, int rows, const uint32_t * masks_host,
+                               const int32_t * history_host, int64_t history_stride,
+                               const int32_t * history_len_host, const fns_b200_params * params_host, void * stream);
+/* Engine::pick_wait (src/engine.cu:849-852): waits for the oldest pick in flight; tokens_host[rows]. */
+int fns_b200_engine_pick_wait(fns_b200_engine * e, int32_t * tokens_host);
+/* Device copy of the tokens of the latest pick (the reference's io_ + 2), for a forward pass that is queued
+ * before the host has seen the token (Engine::step_next, src/engine.cu:796-800). */
+const int32_t * fns_b200_engine_device_tokens(const fns_b200_engine * e);
+/* Engine::reset_presence (src/engine.cu:854-860): forgets the device-side history of every session. */
+int fns_b200_engine_reset(fns_b200_engine * e, void * stream);
+/* Engine::presence_commit / k::presence_mark (src/engine.cu:843,862-866): appends, per session, the first
+ * counts_host[r] of tokens [rows][tokens_stride] (device memory; ids < 0 are skipped) to the device-side
+ * history.  counts_host NULL: one token per session. */
+int fns_b200_engine_append(fns_b200_engine * e, const int32_t * tokens, int64_t tokens_stride, int rows,
+                           const int32_t * counts_host, void * stream);
+/* Engine::verify, sampler part (src/engine.cu:733-765), for `windows` windows of n_draft + 1 rows, with the
+ * accept rule of fns-serve (tools/fns_serve/fns_serve.cpp:492-508) computed on the device.  Synchronous, like the
+ * reference.  draft_host [windows][n_draft]; masks_host NULL or [windows * (n_draft + 1)][words];
+ * tokens_host [windows][n_draft + 1]; accept_host [windows]. */
+int fns_b200_engine_verify(fns_b200_engine * e, const void * logits, int dtype, int64_t row_stride, int windows,
+                           int n_draft, const int32_t * draft_host, const uint32_t * masks_host,
+                           const fns_b200_params * params_host, int32_t * tokens_host, int32_t * accept_host,
+                           void * stream);
+/* Prompt-lookup draft (include/fns/lookup.h:12-27) on the host: the continuation of the latest earlier
+ * occurrence of the final n-gram of the history, n = 4 down to 2.  Returns the number of ids written. */
+int fns_b200_lookup_draft(const int32_t * history_host, int n_history, int want, int32_t * out_host);
+
 /* Launch geometry chosen for a call (slices per row, threads, dynamic shared memory of the select kernel),
  * for benchmarks and tests. */
 int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int history_bound, int * slices,

@@ -1,0 +1,27 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle.binding import Oracle
+
+    return Oracle()
+
+
+@pytest.fixture(scope="session")
+def library_path():
+    """Builds the CUDA library if the sources are newer (nvcc cross-compiles without a GPU)."""
+    from flintnsteel_b200 import build
+
+    return build.build()
