@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the sampler hot path (logits -> token) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("sessions256"): 256 independent sessions per GPU per step, V = 151,936 fp32 logits, xgrammar-style
+bitmask, 2,048-id histories with repetition / presence / frequency penalties, per-row temperature / top-k /
+top-p (the batched configuration of the headline metric).  A step is one pass of the sampler over one batch;
+several distinct batches rotate so that every step's inputs (155 MB of logits per batch, larger than the
+126 MB L2) come from HBM.  Rows shard across GPUs with no data-path collective ("weak" scaling: 256 rows per
+GPU).  One JSON line is printed by rank 0.
+
+--impl reference times the CPU restatement of the reference's sampler (oracle/, OpenMP over rows on every
+host core) on the same workload, a bounded sample per step; the reference's own CUDA kernels, recompiled for
+sm_100a, are timed beside it (they are GPU code, so they are reported as an extra, not as the CPU arm).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sampler rows/s (V=151936 fp32, mask+penalties+top-k/p, 256 sessions per GPU)"
+WORKLOAD = "sessions256"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def pinned(a: np.ndarray):
+    import torch
+
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return t.pin_memory()
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from flintnsteel_b200 import workloads as wl
+    from flintnsteel_b200.sampler import Engine, Sampler, params_to_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl b200 needs a CUDA device: the sampler has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    rows, K, W = args.rows, args.steps, args.warmup
+
+    # ---- inputs: `batches` distinct 256-row batches per rank, resident in HBM --------------------------------
+    host = [wl.session_batch(seed=1000 * rank + b, rows=rows) for b in range(args.batches)]
+    vocab = host[0].vocab
+    row_bytes = host[0].row_bytes()
+    dev_in = []
+    for w in host:
+        dev_in.append(dict(
+            logits=torch.from_numpy(w.logits).to(dev), masks=torch.from_numpy(w.masks.view(np.int32)).to(dev),
+            history=torch.from_numpy(w.history).to(dev), history_len=torch.from_numpy(w.history_len).to(dev),
+            params=params_to_device(w.params, dev)))
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    sampler = Sampler(local, max_rows=rows, max_vocab=vocab, k_cap=64, max_history=host[0].history.shape[1])
+
+    def step(i):
+        d = dev_in[i % len(dev_in)]
+        sampler.sample_rows(d["logits"], d["params"], out, masks=d["masks"], history=d["history"],
+                            history_len=d["history_len"])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(i)
+    barrier()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+        time.sleep(0.25)
+    # ---- timed region: exactly K steps, device time, max over ranks ----------------------------------------
+    launches0 = sampler.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    launches = sampler.launch_count() - launches0
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    # a longer untimed stretch of the same steps so that the clock record has samples under load
+    if rank == 0:
+        t_end = time.time() + 1.0
+        i = 0
+        while time.time() < t_end:
+            step(i)
+            i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+    clock_info = clocks.stop() if rank == 0 else None
+    sampler.device_status()
+
+    # ---- the dominant kernel alone: CUDA events around each select launch, same steps ----------------------
+    sampler.profile_begin(K)
+    for i in range(K):
+        step(i)
+    sel_ms, fin_ms, calls = sampler.profile_end()
+    peak, peak_kind = measured_peaks()
+    sel_avg_s = sel_ms / max(calls, 1) / 1e3
+    achieved = rows * row_bytes / sel_avg_s / 1e9 if sel_avg_s > 0 else 0.0
+
+    # ---- end to end through the engine glue: host buffers in, tokens out to the host, every step -----------
+    eng = Engine(local, max_rows=rows, vocab=vocab, k_cap=64, max_history=host[0].history.shape[1])
+    host_pin = [dict(logits=pinned(w.logits), masks=pinned(w.masks.view(np.int32)), history=pinned(w.history),
+                     history_len=pinned(w.history_len), params=pinned(w.params.view(np.uint8))) for w in host[:2]]
+
+    def e2e(steps, logits_on_host):
+        for warm in range(2):
+            h, d = host_pin[warm % 2], dev_in[warm % 2]
+            eng.pick(h["logits"] if logits_on_host else d["logits"], h["params"], masks_host=h["masks"],
+                     history_host=h["history"], history_len_host=h["history_len"], logits_on_host=logits_on_host)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            h, d = host_pin[i % 2], dev_in[i % 2]
+            eng.pick(h["logits"] if logits_on_host else d["logits"], h["params"], masks_host=h["masks"],
+                     history_host=h["history"], history_len_host=h["history_len"], logits_on_host=logits_on_host)
+        b.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return world * rows * steps / (float(t.item()) / 1e3)
+
+    side_bytes = rows * (host[0].masks.shape[1] * 4 + host[0].history.shape[1] * 4 + 4 + 48)
+    e2e_steps = max(3, min(K, 20))
+    e2e_host = e2e(e2e_steps, True)
+    e2e_engine = e2e(max(3, min(K, 100)), False)
+
+    result = {
+        "metric": METRIC, "value": world * rows * K / (total_ms / 1e3), "unit": "rows/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "vocab": vocab, "k_cap": 64,
+                   "history_ids": int(host[0].history.shape[1]), "batches_rotated": len(dev_in),
+                   "l2": f"{len(dev_in)} distinct batches of {rows * row_bytes / 1e6:.0f} MB rotate; each exceeds the 126 MB L2",
+                   "parallelism": f"rows{world}"},
+        "us_per_row": total_ms * 1e3 / (K * rows),
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "k_select", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBps_nominal": achieved / 8000.0,
+                     "bytes_per_launch": rows * row_bytes, "avg_launch_us": sel_avg_s * 1e6,
+                     "finalize_avg_launch_us": fin_ms / max(calls, 1) * 1e3, "traffic": args.traffic},
+        "e2e": {"value": e2e_host, "unit": "rows/s", "h2d_bytes_per_step": int(rows * vocab * 4 + side_bytes),
+                "d2h_bytes_per_step": rows * 4, "steps": e2e_steps,
+                "note": "engine pick (pick_async + pick_wait): logits, masks, histories and parameters all copied "
+                        "from pinned host memory every step, tokens read back"},
+        "e2e_engine": {"value": e2e_engine, "unit": "rows/s", "h2d_bytes_per_step": int(side_bytes),
+                       "d2h_bytes_per_step": rows * 4,
+                       "note": "as the reference's Engine::pick_async is used: logits already on the GPU (the LM "
+                               "head wrote them), masks / histories / parameters from host memory, tokens back"},
+    }
+    if rank == 0:
+        result["clocks"] = clock_info
+    if rank == 0 and not args.skip_extras:
+        result["batch1"] = batch1_latency(torch, dev, local)
+    if rank == 0 and world == 1 and not args.skip_extras:
+        result["cpu_baseline"] = cpu_baseline(host[0], budget_s=args.cpu_seconds)
+        result["reference_gpu_kernels"] = reference_gpu(torch, dev, host[0], dev_in[0])
+    if world > 1 and not args.skip_extras:
+        vs = vocab_sharded(torch, dist, dev, local, rank, world)
+        if rank == 0:
+            result["vocab_sharded"] = vs
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def batch1_latency(torch, dev, local):
+    """Device time per row at batch 1: a CUDA graph of 50 back-to-back calls replayed 40 times (no host launch
+    gaps), and plain stream launches for comparison."""
+    from flintnsteel_b200 import workloads as wl
+    from flintnsteel_b200.sampler import Sampler, params_to_device
+
+    res = {}
+    cases = {"single_row_T0.7_k40_p0.95_rep1.1_h512": wl.single_row(), "single_row_greedy": wl.single_row(greedy=True),
+             "grammar_row_mask1.5pct_h4096_allpen_k20": wl.grammar_row()}
+    for name, w in cases.items():
+        s = Sampler(local, max_rows=1, max_vocab=w.vocab, k_cap=64, max_history=4096)
+        lg = torch.from_numpy(w.logits).to(dev)
+        masks = None if w.masks is None else torch.from_numpy(w.masks.view(np.int32)).to(dev)
+        hist, hl = torch.from_numpy(w.history).to(dev), torch.from_numpy(w.history_len).to(dev)
+        pd = params_to_device(w.params, dev)
+        out = torch.empty(1, dtype=torch.int32, device=dev)
+
+        def call():
+            s.sample_rows(lg, pd, out, masks=masks, history=hist, history_len=hl)
+
+        for _ in range(5):
+            call()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            call()
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(50):
+                    call()
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(40):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        graph_us = a.elapsed_time(b) * 1e3 / (40 * 50)
+        a.record()
+        for _ in range(200):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        res[name] = {"us_per_row_graph": graph_us, "us_per_row_stream": a.elapsed_time(b) * 1e3 / 200,
+                     "bytes_per_row": w.row_bytes(), "plan": s.plan(0, w.vocab, 1, w.history.shape[1])}
+        s.close()
+    return res
+
+
+def cpu_baseline(w, budget_s: float):
+    """The CPU oracle (a port of the reference's sampler, not the product) on this host's cores, same rows."""
+    from oracle.binding import Oracle
+
+    o = Oracle()
+    x = w.logits
+    t0, done, threads = time.time(), 0, 1
+    n = min(32, w.rows)
+    while time.time() - t0 < budget_s:
+        lo = done % w.rows
+        hi = min(w.rows, lo + n)
+        _, threads = o.sample_rows(x[lo:hi], w.params[lo:hi], 64, w.masks[lo:hi], w.history[lo:hi], w.history_len[lo:hi])
+        done += hi - lo
+    dt = time.time() - t0
+    return {"value": done / dt, "unit": "rows/s", "cores": threads, "kind": "port",
+            "sample": f"{done} rows of the same batch in {dt:.1f} s, OpenMP over rows"}
+
+
+def reference_gpu(torch, dev, w, d):
+    """The reference's own CUDA sampler (src/kernels.cu, unmodified, built for sm_100a) on this GPU: one row per
+    call, two launches per row.  It has no repetition / frequency terms, so it runs the same rows and masks
+    without penalties: the same memory traffic and the same selection work."""
+    try:
+        from oracle.binding import RefGpu
+
+        ref = RefGpu()
+    except Exception as exc:  # the checker library is optional for the benchmark
+        return {"unavailable": str(exc)}
+    out = torch.empty(w.rows, dtype=torch.int32, device=dev)
+    ref.sample_rows(d["logits"], d["masks"], w.params, out)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    ref.sample_rows(d["logits"], d["masks"], w.params, out)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    return {"value": w.rows / (ms / 1e3), "unit": "rows/s", "us_per_row": ms * 1e3 / w.rows,
+            "note": "reference kernels recompiled for sm_100a, row by row on one stream (they are not re-entrant)"}
+
+
+def vocab_sharded(torch, dist, dev, local, rank, world):
+    """64 rows x V = 262,144 bf16 split evenly by vocabulary: per-shard top-1024, one NCCL all-gather of
+    (value, id) candidates, merge + draw on every rank."""
+    from flintnsteel_b200 import workloads as wl
+    from flintnsteel_b200.dispatch import VocabSharded
+    from flintnsteel_b200.sampler import Sampler, params_to_device
+
+    w = wl.large_vocab(seed=0, rows=64)
+    s = Sampler(local, max_rows=w.rows, max_vocab=w.vocab, k_cap=1024, max_history=0)
+    vs = VocabSharded(s, w.vocab, 1024, rank, world)
+    lo, hi = vs.lo, vs.hi
+    lg = torch.from_numpy(np.ascontiguousarray(w.logits[:, lo:hi]).view(np.int16)).to(dev).view(torch.bfloat16)
+    masks = torch.from_numpy(np.ascontiguousarray(w.masks[:, lo // 32:(hi + 31) // 32]).view(np.int32)).to(dev)
+    pd = params_to_device(w.params, dev)
+    out = torch.empty(w.rows, dtype=torch.int32, device=dev)
+    for _ in range(5):
+        vs.sample(lg, pd, out, masks_shard=masks)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = 50
+    a.record()
+    for _ in range(steps):
+        vs.sample(lg, pd, out, masks_shard=masks)
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = out.clone()
+    dist.broadcast(same, 0)
+    agree = bool(torch.equal(same, out))
+    flag = torch.tensor([1 if agree else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ms = float(t.item()) / steps
+    return {"rows_per_s": w.rows / (ms / 1e3), "ms_per_step": ms, "rows": w.rows, "vocab": w.vocab, "k": 1024,
+            "allgather_bytes_per_rank": w.rows * 1024 * 8, "all_ranks_agree": bool(flag.item()),
+            "scaling": "strong (the vocabulary is split)"}
+
+
+def run_reference(args):
+    """CPU arm: the oracle port with every host thread, on bounded samples of the same workload."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from flintnsteel_b200 import workloads as wl
+    from oracle.binding import Oracle
+
+    o = Oracle()
+    sample_rows = 64
+    w = wl.session_batch(seed=0, rows=sample_rows)
+    threads = 1
+    for _ in range(max(args.warmup, 1)):
+        _, threads = o.sample_rows(w.logits[:16], w.params[:16], 64, w.masks[:16], w.history[:16], w.history_len[:16])
+    K = min(args.steps, 40)
+    t0 = time.time()
+    for _ in range(K):
+        o.sample_rows(w.logits, w.params, 64, w.masks, w.history, w.history_len)
+    dt = time.time() - t0
+    value = sample_rows * K / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": K,
+        "warmup": max(args.warmup, 1), "ms_per_step": dt / K * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_step": sample_rows, "vocab": w.vocab, "k_cap": 64,
+                   "history_ids": int(w.history.shape[1]),
+                   "note": "each step is a 64-row sample of the 256-session batch; the reference's sampler is CUDA "
+                           "code, its CPU form is the restatement in oracle/fns_oracle.c"},
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
+                         "sample": f"{K} steps of {sample_rows} rows, OpenMP over rows"},
+        "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            from flintnsteel_b200.sampler import params_to_device  # noqa: F401  (torch plumbing only)
+
+            dev = torch.device("cuda:0")
+            d = {"logits": torch.from_numpy(w.logits).to(dev), "masks": torch.from_numpy(w.masks.view(np.int32)).to(dev)}
+            line["reference_gpu_kernels"] = reference_gpu(torch, dev, w, d)
+    except Exception as exc:
+        line["reference_gpu_kernels"] = {"unavailable": str(exc)}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rows", type=int, default=256)
+    ap.add_argument("--batches", type=int, default=4)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--skip-extras", action="store_true", help="only the headline numbers (for profiler runs)")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="dram bytes per select launch from an ncu capture (see profiles/), echoed into the line")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

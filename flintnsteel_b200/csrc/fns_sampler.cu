@@ -308,11 +308,12 @@ __global__ void __launch_bounds__(kThreads) k_select(const SelectArgs a) {
 
 // ---- finalize ---------------------------------------------------------------------------------------------
 struct FinalArgs {
-    const uint64_t * keys;        // internal lists [rows][lists][stride] (sorted keys, 0 = empty), or
-    const fns_b200_cand * cands;  // external lists [rows][lists][stride]
+    const uint64_t * keys;        // internal lists (sorted keys, 0 = empty), or
+    const fns_b200_cand * cands;  // external lists; entry j of list l of row r at r * row_stride + l * list_stride + j
     int lists;
-    int list_len;  // entries to read from each list (<= stride)
-    int stride;
+    int list_len;  // entries to read from each list
+    int64_t list_stride;
+    int64_t row_stride;
     int k_cap;
     int n_draft;
     const fns_b200_params * params;
@@ -357,10 +358,10 @@ __global__ void __launch_bounds__(kThreads) k_finalize(const FinalArgs a) {
     __syncthreads();
     // Gather the non-empty keys (their order does not matter: the selection below is by key alone, which makes
     // the result independent of how many slices or shards produced the lists).
-    const size_t row_base = (size_t) row * a.lists * a.stride;
+    const size_t row_base = (size_t) row * a.row_stride;
     for (int i = tid; i < a.lists * take_len; i += kThreads) {
         const int l = i / take_len, j = i - l * take_len;
-        const size_t at = row_base + (size_t) l * a.stride + j;
+        const size_t at = row_base + (size_t) l * a.list_stride + j;
         const uint64_t key = a.keys ? a.keys[at] : cand_to_key(a.cands[at]);
         if (key != 0ull) buf[atomicAdd(&sh.n_keys, 1u)] = key;
     }
@@ -647,7 +648,8 @@ int run_final_internal(fns_b200_sampler * s, const Plan & pl, int rows, int n_dr
     f.keys = s->cand;
     f.lists = pl.slices;
     f.list_len = s->k_cap;
-    f.stride = s->k_cap;
+    f.list_stride = s->k_cap;
+    f.row_stride = (int64_t) pl.slices * s->k_cap;
     f.k_cap = s->k_cap;
     f.n_draft = n_draft;
     f.params = params;
@@ -830,19 +832,21 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     return run_final_internal(s, pl, rows, 0, params, nullptr, nullptr, out_cands, (cudaStream_t) stream);
 }
 
-int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len, int rows,
-                           const fns_b200_params * params, int32_t * out_tokens, fns_b200_cand * out_cands,
-                           void * stream) {
+int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len,
+                           int64_t list_stride, int64_t row_stride, int rows, const fns_b200_params * params,
+                           int32_t * out_tokens, fns_b200_cand * out_cands, void * stream) {
     if (!s) return FNS_B200_ERR_ARG;
     if (!cands || !params || (!out_tokens && !out_cands)) return fail(s, FNS_B200_ERR_ARG, "cands / params null, or no output");
     if (lists <= 0 || list_len <= 0 || rows <= 0 || (int64_t) lists * list_len > kMaxMergeKeys)
         return fail(s, FNS_B200_ERR_ARG, "lists * list_len outside (0, 8192]");
+    if (list_stride < 0 || row_stride < 0) return fail(s, FNS_B200_ERR_ARG, "negative stride");
     DeviceGuard g(s->device);
     FinalArgs f{};
     f.cands = cands;
     f.lists = lists;
     f.list_len = list_len;
-    f.stride = list_len;
+    f.list_stride = list_stride;
+    f.row_stride = row_stride;
     f.k_cap = s->k_cap;
     f.n_draft = 0;
     f.params = params;

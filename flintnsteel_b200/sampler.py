@@ -114,7 +114,7 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_sample_rows.argtypes = [vp, vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
     lib.fns_b200_sample_one.argtypes = [vp, vp, i32, i32, vp, vp, i32, vp, vp, vp]
     lib.fns_b200_select_rows.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
-    lib.fns_b200_finalize_rows.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp]
+    lib.fns_b200_finalize_rows.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp, vp, vp, vp]
     lib.fns_b200_verify_accept.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, vp, i64, vp, i64, vp, vp, vp, vp, vp]
     lib.fns_b200_presence_apply.argtypes = [vp, vp, i32, f32, vp]
     lib.fns_b200_presence_mark.argtypes = [vp, vp, vp]
@@ -260,10 +260,14 @@ class Sampler:
             _ptr(params), _ptr(out_cands), _stream()))
         return out_cands
 
-    def finalize_rows(self, cands, lists: int, list_len: int, rows: int, params, out_tokens=None, out_cands=None):
+    def finalize_rows(self, cands, lists: int, list_len: int, rows: int, params, out_tokens=None, out_cands=None,
+                      list_stride=None, row_stride=None):
+        """Default layout [rows][lists][list_len]; pass strides (in entries) for anything else."""
+        list_stride = list_len if list_stride is None else list_stride
+        row_stride = lists * list_len if row_stride is None else row_stride
         self._check(self.lib.fns_b200_finalize_rows(
-            self.handle, _ptr(cands), lists, list_len, rows, _ptr(params), _ptr(out_tokens), _ptr(out_cands),
-            _stream()))
+            self.handle, _ptr(cands), lists, list_len, list_stride, row_stride, rows, _ptr(params),
+            _ptr(out_tokens), _ptr(out_cands), _stream()))
 
     def verify_accept(self, logits, draft, params, out_tokens, out_accept, masks=None, history=None,
                       history_len=None, vocab=None):

@@ -120,11 +120,14 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
 /* Second half of the path: merge `lists` candidate lists per row (e.g. one per vocabulary shard, gathered into
  * local memory) and draw.  This is k_sample (src/kernels.cu:671-721): selection rounds over the slices'
  * candidates, then softmax / top-p / temperature / Philox draw.
- *   cands        [rows][lists][list_len]; lists * list_len <= 8192
+ *   cands        entry j of list l of row r is cands[r * row_stride + l * list_stride + j] (strides in entries);
+ *                lists * list_len <= 8192.  [rows][lists][list_len] is (row_stride = lists * list_len,
+ *                list_stride = list_len); an all-gather of per-shard [rows][k_cap] blocks is
+ *                (row_stride = k_cap, list_stride = rows * k_cap)
  *   out_cands    NULL, or [rows][k_cap]: the merged list, for inspection */
-int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len, int rows,
-                           const fns_b200_params * params, int32_t * out_tokens, fns_b200_cand * out_cands,
-                           void * stream);
+int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len,
+                           int64_t list_stride, int64_t row_stride, int rows, const fns_b200_params * params,
+                           int32_t * out_tokens, fns_b200_cand * out_cands, void * stream);
 
 /* Speculative verification of `windows` windows of W = n_draft + 1 logit rows each (row = window * W + c).
  * Replaces the per-column loop of Engine::verify (src/engine.cu:750-757: k::presence_apply_col + k::argmax /
