@@ -1,16 +1,19 @@
 // fns_sampler.cu - the sampler kernels for sm_100a and the C ABI declared in include/fns_b200.h.
 //
-// Two kernels per call, both HBM-streaming / latency work with no contraction in it (no tensor cores):
+// HBM-streaming / latency work with no contraction in it (no tensor cores):
 //
 //   k_select   grid (slices, rows).  One pass over a slice of one row of logits: 128-bit coalesced loads, the
 //              grammar bitmask and the penalty history folded into a shared-memory bit set, and an exact
 //              top-k of the slice by threshold filtering: elements that beat the current k-th best key are
-//              appended to a shared buffer; when the buffer passes its high-water mark the block radix-selects
-//              the best k and raises the threshold.  Replaces k_topk_part of the reference
-//              (src/kernels.cu:624-648), which rescans its slice k times, and k_presence_apply / _col
-//              (src/kernels.cu:724-742), which rewrite the whole row in place.
-//   k_finalize grid (rows).  Merges the slices' candidates, then does the candidate softmax, top-p / min-p cut,
-//              temperature weights and Philox draw of k_sample's tail (src/kernels.cu:698-720).
+//              appended to a shared buffer; when the buffer fills, the block radix-selects the best k and
+//              raises the threshold.  Regions that the bit set masks out are skipped without touching the
+//              logits.  Replaces k_topk_part of the reference (src/kernels.cu:624-648), which rescans its slice
+//              k times, and k_presence_apply / _col (src/kernels.cu:724-742), which rewrite the whole row.
+//              The last block of a row to finish (a ticket, no waiting) merges the slices' candidates and
+//              draws the token, so a whole call is ONE launch.
+//   k_finalize grid (rows).  The same merge + draw as a kernel of its own, for candidate lists that come from
+//              elsewhere (vocabulary shards gathered from other GPUs): k_sample of the reference
+//              (src/kernels.cu:671-721).
 //
 // Nothing here waits on another block, so there is no spin loop anywhere in the sampler.
 #include "fns_device.cuh"
@@ -22,11 +25,26 @@
 
 namespace fnsb {
 
+#ifdef FNS_PHASE_TIMING  // development aid: block time per phase, summed over blocks (thread 0's clock)
+__device__ unsigned long long g_phase[8];
+#define FNS_PHASE_BEGIN long long ph_t = clock64();
+#define FNS_PHASE(i)                                                           \
+    if (threadIdx.x == 0) {                                                    \
+        const long long ph_n = clock64();                                      \
+        atomicAdd(&g_phase[i], (unsigned long long) (ph_n - ph_t));            \
+        ph_t = ph_n;                                                           \
+    }
+#else
+#define FNS_PHASE_BEGIN
+#define FNS_PHASE(i)
+#endif
+
 constexpr int kHashEmpty = -1;             // 0xffffffff
 constexpr int kMaxMergeKeys = 8192;        // k_finalize holds the lists of one row in shared memory
 constexpr int kMaxSlices = 128;
 constexpr int kMaxSliceLen = 65536;        // a history table entry keeps the in-slice offset in 16 bits
-constexpr int kSliceAlign = 1024;          // slice length granularity (elements); keeps loads 16-byte aligned
+constexpr int kSliceAlign = 4096;          // slice length granularity (elements): one epoch of a block
+constexpr int kEpochElems = 16;            // elements per thread between two block votes
 
 struct SelectArgs {
     const void * logits;
@@ -45,10 +63,13 @@ struct SelectArgs {
     int k_cap;
     int slices;
     int slice_len;
-    int cap;         // candidate buffer entries
-    int high_water;  // compaction trigger; cap - high_water >= elements one block iteration can append
+    int cap;         // candidate buffer entries (>= 4 * k_cap)
+    int trigger;     // compact when the buffer holds this many, to keep the threshold fresh
     int ht_size;     // history table slots (power of two, multiple of kThreads), 0: no table
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
+    unsigned * tickets;         // [rows], zero between launches; null: no fused finalize
+    int32_t * out_tokens;       // fused finalize: [rows], may be null
+    fns_b200_cand * out_cands;  // fused finalize: [rows][k_cap], may be null
     int * err;
 };
 
@@ -56,7 +77,13 @@ struct SelectShared {
     SelectScratch sc;
     uint64_t thr_key;   // keys below this cannot be among the slice's best k
     float thr_value;    // x < thr_value  =>  key < thr_key
-    uint32_t n_cand;
+    uint32_t n_cand;    // append cursor; may run past cap (the excess was not stored: see `lost`)
+    uint32_t n_keys;
+    int keep;
+    int is_last;
+    uint32_t epoch_mask;  // epochs of the slice that have an allowed element
+    uint32_t n_list;      // occupied slots of the history table
+    __align__(16) uint32_t warp_bound[kThreads / 32];  // per warp: a value that r of its lanes have reached
     uint64_t red[kThreads / 32];
 };
 
@@ -85,10 +112,21 @@ __device__ __forceinline__ void load_vec(const T * p, float (&out)[VEC]) {
     }
 }
 
-// Keeps the best k keys of buf[0 .. n_cand) in buf[0 .. k) and raises the threshold.  All threads; block
+// One key into the candidate buffer.  False when the buffer is full: the caller remembers the element and
+// offers it again after the next compaction.
+__device__ __forceinline__ bool push(uint64_t key, uint64_t * buf, SelectShared & sh, int cap) {
+    const uint32_t pos = atomicAdd(&sh.n_cand, 1u);
+    if (pos < (uint32_t) cap) {
+        buf[pos] = key;
+        return true;
+    }
+    return false;
+}
+
+// Keeps the best k keys of the buffer in buf[0 .. k) and raises the threshold.  All threads; the block is
 // synchronised on entry (every append is visible) and on exit.
-__device__ void compact(uint64_t * buf, uint64_t * sel, int k, SelectShared & sh) {
-    const int n = (int) sh.n_cand;
+__device__ void compact(uint64_t * buf, uint64_t * sel, int k, int cap, SelectShared & sh) {
+    const int n = (int) min(sh.n_cand, (uint32_t) cap);
     if (n <= k) return;
     const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
     const int got = block_take(buf, n, k, tau, sel, sh.sc);
@@ -101,187 +139,524 @@ __device__ void compact(uint64_t * buf, uint64_t * sel, int k, SelectShared & sh
     __syncthreads();
 }
 
-template <typename T, int VEC, int UNROLL>
-__global__ void __launch_bounds__(kThreads) k_select(const SelectArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int row = blockIdx.y, slice = blockIdx.x;
-    const int W = a.n_draft + 1, win = row / W, col = row - win * W;
-    const fns_b200_params p = a.params ? a.params[win] : a.p0;
-    const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
-    const int lo = slice * a.slice_len;
-    const int n_s = min(a.vocab, lo + a.slice_len) - lo;
-    uint64_t * out = a.cand + ((size_t) row * a.slices + slice) * a.k_cap;
-    if (n_s <= 0) {
-        for (int j = tid; j < k; j += kThreads) out[j] = 0ull;
+// The candidate softmax, top-p / min-p cut, temperature weights and Philox draw of k_sample
+// (src/kernels.cu:698-720) for one row.  buf holds `lists` lists of `len` keys each, every list sorted in the
+// total order with its empty slots (0) at the end; they are first merged into the best k, sorted (the selection
+// rounds of src/kernels.cu:680-695): with few lists by ranking every key (its position plus, by binary search,
+// the number of larger keys in each other list; no barrier), else by radix selection.  All kThreads threads,
+// block synchronised on entry.  p.counter is the counter of this row.  exp and the quotients are per-element and
+// run in parallel; the three running sums keep the reference's left-to-right order: `sum` then `cum` on thread
+// 0, the weight prefix (which is both wsum and the acc of the inverse-CDF walk) on thread 32.
+__device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel, uint64_t * sorted, double * pj,
+                             double * acc, SelectScratch & sc, int & sh_keep, const fns_b200_params & p, int k,
+                             int k_cap, int32_t * out_token, fns_b200_cand * out_cands) {
+    const int tid = threadIdx.x;
+    const int total = lists * len;
+    int nk;
+    if (lists <= 8) {
+        for (int j = tid; j < k_cap; j += kThreads) sorted[j] = 0ull;
+        if (tid == 0) sc.count = 0u;
+        __syncthreads();
+        int mine = 0;
+        for (int i = tid; i < total; i += kThreads) {
+            const uint64_t key = buf[i];
+            if (key == 0ull) continue;
+            ++mine;
+            const int l = i / len;
+            int rank = i - l * len;
+            for (int o = 0; o < lists && rank < k; ++o) {
+                if (o == l) continue;
+                const uint64_t * other = buf + o * len;
+                int lo = 0, hi = len;  // number of keys of `other` that are larger (it is sorted descending)
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (other[mid] > key) lo = mid + 1;
+                    else hi = mid;
+                }
+                rank += lo;
+            }
+            if (rank < k) sorted[rank] = key;
+        }
+        if (mine) atomicAdd(&sc.count, (uint32_t) mine);
+        __syncthreads();
+        nk = (int) min(sc.count, (uint32_t) k);  // fewer than k allowed tokens: src/kernels.cu:698-699
+    } else {
+        if (tid == 0) sc.count = 0u;
+        __syncthreads();
+        // squeeze out the empty slots (the order does not matter to the selection)
+        for (int base = 0; base < total; base += kThreads) {
+            const int i = base + tid;
+            const uint64_t key = i < total ? buf[i] : 0ull;
+            __syncthreads();
+            if (key != 0ull) buf[atomicAdd(&sc.count, 1u)] = key;
+            __syncthreads();
+        }
+        const int n = (int) sc.count;
+        __syncthreads();
+        const uint64_t tau = block_kth_key(buf, n, k, sc);
+        nk = block_take(buf, n, k, tau, sel, sc);  // fewer than k allowed tokens: src/kernels.cu:698-699
+        for (int j = nk + tid; j < k_cap; j += kThreads) sorted[j] = 0ull;
+        block_rank_sort(sel, nk, sorted);
+        __syncthreads();
+    }
+    if (out_cands)
+        for (int j = tid; j < k_cap; j += kThreads) out_cands[j] = key_to_cand(sorted[j]);
+    if (!out_token) return;
+    if (nk == 0) {
+        if (tid == 0) *out_token = -1;
         return;
     }
-    // shared memory: candidate buffer | selection staging | slice bit set | history table | scalars
+    if (p.temperature <= 0.0f || nk == 1) {
+        if (tid == 0) *out_token = key_id(sorted[0]);
+        return;
+    }
+    const double v0 = (double) key_value(sorted[0]);
+    double my_p = 0.0;
+    if (tid < nk) {  // nk <= kThreads in the reference-compatible range; larger k loops below
+        const double d = (double) key_value(sorted[tid]) - v0;
+        my_p = exp(d);
+        pj[tid] = my_p;
+        acc[tid] = exp(d / p.temperature);
+    }
+    for (int j = tid + kThreads; j < nk; j += kThreads) {
+        const double d = (double) key_value(sorted[j]) - v0;
+        pj[j] = exp(d);
+        acc[j] = exp(d / p.temperature);
+    }
+    __syncthreads();
+    double * qj = reinterpret_cast<double *>(sel);  // p_j / sum, in the staging area (k_cap doubles)
+    if (tid == 0) {
+        double sum = 0.0;
+        for (int j = 0; j < nk; ++j) sum += pj[j];
+        *reinterpret_cast<volatile double *>(&sc.hist[0]) = sum;
+    } else if (tid == 32) {
+        double run = 0.0;
+        for (int j = 0; j < nk; ++j) {
+            run += acc[j];
+            acc[j] = run;
+        }
+    }
+    __syncthreads();
+    {
+        const double sum = *reinterpret_cast<volatile double *>(&sc.hist[0]);
+        for (int j = tid; j < nk; j += kThreads) qj[j] = pj[j] / sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int keep = nk;
+        double cum = 0.0;
+        for (int j = 0; j < nk; ++j) {
+            cum += qj[j];
+            if (cum >= p.top_p) { keep = j + 1; break; }
+        }
+        if (p.min_p > 0.0f) {
+            int m = 1;
+            while (m < keep && pj[m] >= (double) p.min_p) ++m;
+            keep = m;
+        }
+        const double wsum = acc[keep - 1];
+        const double u = philox_uniform(p.seed, p.counter) * wsum;
+        int pick = keep - 1;
+        for (int j = 0; j < keep; ++j)
+            if (u < acc[j]) { pick = j; break; }
+        *out_token = key_id(sorted[pick]);
+        sh_keep = keep;
+    }
+}
+
+// Largest float of the allowed, finite elements of one vector (-inf if none).  NaN never wins an fmaxf and
+// fails the `<= FLT_MAX` test; +inf is never a candidate (src/kernels.cu:629-639).
+template <int VEC>
+__device__ __forceinline__ float vector_max(const float (&xv)[VEC], uint32_t bits) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) m = fmaxf(m, ((bits >> j) & 1u) ? xv[j] : -INFINITY);
+    if (m <= FLT_MAX) return m;  // the common case: no +inf among the allowed elements
+    m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+        if (((bits >> j) & 1u) && xv[j] <= FLT_MAX) m = fmaxf(m, xv[j]);
+    return m;
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
+    constexpr int NV = kEpochElems / VEC;            // vectors per thread per epoch
+    constexpr int FPE = NV < 4 ? NV : 4;             // flags per thread per epoch; a flag covers NV / FPE vectors
+    constexpr int VPF = NV / FPE;
+    constexpr int kEpoch = kThreads * kEpochElems;   // elements per block per epoch (slice_len is a multiple)
+    constexpr int kWarps = kThreads / 32;
+    constexpr uint32_t kVecBits = VEC == 32 ? 0xffffffffu : (1u << VEC) - 1u;
+    constexpr int kWordsPerVec = kThreads * VEC / 32;  // bit-set words between two vectors of one thread
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int W = a.n_draft + 1, win = row / W, col = row - win * W;
+    fns_b200_params p = a.params ? a.params[win] : a.p0;
+    const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
+    const int lo = slice * a.slice_len;
+    const int n_s = max(0, min(a.vocab, lo + a.slice_len) - lo);
+    uint64_t * out = a.cand + ((size_t) row * a.slices + slice) * a.k_cap;
+
+    // shared memory: candidate buffer | selection staging | sorted | p, acc (fp64) | slice bit set | history table
+    // | list of the table's occupied slots
     uint64_t * buf = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t * sel = buf + a.cap;
-    uint32_t * eff = reinterpret_cast<uint32_t *>(sel + a.k_cap);
+    uint64_t * sorted = sel + a.k_cap;
+    double * pj = reinterpret_cast<double *>(sorted + a.k_cap);
+    double * acc = pj + a.k_cap;
+    uint32_t * eff = reinterpret_cast<uint32_t *>(acc + a.k_cap);
     int * htab = reinterpret_cast<int *>(eff + a.slice_len / 32);
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(htab + a.ht_size);
+    int * hlist = htab + a.ht_size;
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(hlist + a.ht_size / 2);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
+    const uint32_t id0 = (uint32_t) (a.id_base + lo);
 
-    // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
-    // streaming loop needs no other bounds handling for the mask.
-    const int words = (n_s + 31) >> 5;
-    for (int w = tid; w < words; w += kThreads) {
-        uint32_t m = mrow ? mrow[w] : 0xffffffffu;
-        if (w == words - 1 && (n_s & 31)) m &= (1u << (n_s & 31)) - 1u;
-        eff[w] = m;
-    }
-    for (int i = tid; i < a.ht_size; i += kThreads) htab[i] = kHashEmpty;
-    if (tid == 0) {
-        sh.n_cand = 0u;
-        sh.thr_key = 0ull;
-        sh.thr_value = -FLT_MAX;
-    }
-    uint64_t best = 0ull;  // k == 1: this thread's best key
-    float best_v = -FLT_MAX;
-    __syncthreads();
-
-    // 2. Penalties.  The row's history (plus the draft prefix of a verification column) is scattered into a
-    // shared hash table: in-slice offset -> occurrence count.  Each distinct id is then removed from the bit
-    // set and offered once as a candidate with its penalised value, so the streaming loop below pays nothing
-    // for penalties.  Traffic: 4 bytes per history id (every slice reads the list; it stays in L2).
+    FNS_PHASE_BEGIN
+    // The first history ids are requested before anything else (their addresses do not depend on the row's
+    // history length, which is itself still in flight).
     const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
+    const bool use_hist = any_pen && a.ht_size > 0 && n_s > 0;
+    const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
+    const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
+    int32_t ids0[4] = {-1, -1, -1, -1};
+    if (use_hist && hrow) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = u * kThreads + tid;
+            if (j < (int) a.history_stride) ids0[u] = hrow[j];
+        }
+    }
     int n_hist = 0;
     if (a.history && a.history_len) {
         n_hist = a.history_len[win];
         n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
     }
     const int n_pen = n_hist + (a.draft ? col : 0);
-    if (any_pen && n_pen > 0 && a.ht_size > 0) {
-        const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
-        const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
+
+    // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
+    // streaming loop needs no bounds handling.  A warp's 32 words lie in one epoch (128 words): the epochs that
+    // have any allowed element are collected in sh.epoch_mask, the others are never visited.
+    if (tid == 0) {
+        sh.n_cand = 0u;
+        sh.thr_key = 0ull;
+        sh.epoch_mask = 0u;
+        sh.n_list = 0u;
+    }
+    if (tid < kWarps) sh.warp_bound[tid] = 0u;
+    {
+        int4 * h4 = reinterpret_cast<int4 *>(htab);
+        for (int i = tid; i < a.ht_size / 4; i += kThreads) h4[i] = make_int4(kHashEmpty, kHashEmpty, kHashEmpty, kHashEmpty);
+    }
+    __syncthreads();
+    const int words = (n_s + 31) >> 5;
+    for (int w = tid; w < a.slice_len / 32; w += kThreads) {
+        uint32_t m = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
+        if (w == words - 1 && (n_s & 31)) m &= (1u << (n_s & 31)) - 1u;
+        eff[w] = m;
+        if (__any_sync(kFull, m != 0u) && lane == 0) atomicOr(&sh.epoch_mask, 1u << (w >> 7));
+    }
+    uint64_t best = 0ull;      // k == 1: this thread's best key
+    uint32_t lost = 0u;        // elements of the current round that found the buffer full
+    FNS_PHASE(0)
+
+    // 2. Penalties.  The row's history (plus the draft prefix of a verification column) is scattered into a
+    // shared hash table: in-slice offset -> occurrence count; the thread that claims a slot also appends it to
+    // a list, so the distinct ids can be walked densely afterwards.  Each distinct id is then removed from the
+    // bit set and offered once as a candidate with its penalised value, so the streaming passes pay nothing for
+    // penalties.  Traffic: 4 bytes per history id (every slice reads the list; it stays in L2).
+    if (use_hist && n_pen > 0) {
         const uint32_t hmask = (uint32_t) a.ht_size - 1u;
-        for (int j = tid; j < n_pen; j += kThreads) {
-            const int32_t id = j < n_hist ? hrow[j] : drow[j - n_hist];
-            const uint32_t off = (uint32_t) (id - a.id_base - lo);
-            if (off >= (uint32_t) n_s || id < a.id_base) continue;
-            uint32_t h = (off * 2654435761u) & hmask;
-            for (int probe = 0; probe <= a.ht_size; ++probe) {
-                if (probe == a.ht_size) { atomicExch(a.err, 2); break; }  // table full: cannot happen (load <= 1/2)
-                int cur = htab[h];
-                if (cur == kHashEmpty) {
-                    cur = atomicCAS(&htab[h], kHashEmpty, (int) ((off << 16) | 1u));
-                    if (cur == kHashEmpty) break;
+        for (int j0 = 0; j0 < n_pen; j0 += kThreads * 4) {
+            int32_t ids[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {  // four independent loads in flight
+                const int j = j0 + u * kThreads + tid;
+                if (j0 == 0 && hrow) ids[u] = j < n_hist ? ids0[u] : (j < n_pen ? drow[j - n_hist] : -1);
+                else ids[u] = j < n_hist ? hrow[j] : (j < n_pen ? drow[j - n_hist] : -1);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t off = (uint32_t) (ids[u] - a.id_base - lo);
+                if (off >= (uint32_t) n_s || ids[u] < a.id_base) continue;
+                uint32_t h = (off * 2654435761u) & hmask;
+                for (int probe = 0; probe <= a.ht_size; ++probe) {
+                    if (probe == a.ht_size) { atomicExch(a.err, 2); break; }  // table full: cannot happen (load <= 1/2)
+                    int cur = htab[h];
+                    if (cur == kHashEmpty) {
+                        cur = atomicCAS(&htab[h], kHashEmpty, (int) ((off << 16) | 1u));
+                        if (cur == kHashEmpty) {
+                            hlist[atomicAdd(&sh.n_list, 1u)] = (int) h;
+                            break;
+                        }
+                    }
+                    if (((uint32_t) cur >> 16) == off) {
+                        atomicAdd(&htab[h], 1);
+                        break;
+                    }
+                    h = (h + 1u) & hmask;
                 }
-                if (((uint32_t) cur >> 16) == off) {
-                    atomicAdd(&htab[h], 1);
-                    break;
-                }
-                h = (h + 1u) & hmask;
             }
         }
         __syncthreads();
-        for (int base = 0; base < a.ht_size; base += kThreads) {
-            if (k > 1 && __syncthreads_or(*(volatile uint32_t *) &sh.n_cand > (uint32_t) a.high_water))
-                compact(buf, sel, k, sh);
-            const int e = htab[base + tid];
-            if (e == kHashEmpty) continue;
+        const int n_list = (int) sh.n_list;
+        // penalised key of a table entry; v is the raw logit.  0 if the result is not finite.
+        auto entry_key = [&](int e, float v) -> uint64_t {
             const uint32_t off = (uint32_t) e >> 16;
             const float cnt = (float) ((uint32_t) e & 0xffffu);
-            const uint32_t bit = 1u << (off & 31);
-            const uint32_t old = atomicAnd(&eff[off >> 5], ~bit);
-            if (!(old & bit)) continue;  // not allowed by the grammar mask
-            float v = to_float(x[off]);
             // each step rounded on its own: no fused multiply-add
             v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
             v = __fsub_rn(v, __fmul_rn(p.frequency, cnt));
             v = __fsub_rn(v, p.presence);
-            if (!is_finite(v)) continue;
-            const uint64_t key = make_key(v, (uint32_t) (a.id_base + lo) + off);
-            if (k == 1) {
-                if (key > best) { best = key; best_v = v; }
-            } else if (key >= *(volatile uint64_t *) &sh.thr_key) {
-                const uint32_t pos = atomicAdd(&sh.n_cand, 1u);
-                if (pos < (uint32_t) a.cap) buf[pos] = key;
-                else atomicExch(a.err, 1);
-            }
-        }
-        __syncthreads();
-    }
-
-    // 3. The streaming pass.  Per block iteration every thread takes UNROLL vectors; a vector is touched only
-    // if the bit set allows one of its elements.
-    const int n_vec = (n_s + VEC - 1) / VEC;
-    const uint32_t id0 = (uint32_t) (a.id_base + lo);
-    for (int v0 = 0; v0 < n_vec; v0 += kThreads * UNROLL) {
-        if (k > 1 && __syncthreads_or(*(volatile uint32_t *) &sh.n_cand > (uint32_t) a.high_water))
-            compact(buf, sel, k, sh);
-        float xv[UNROLL][VEC];
-        uint32_t mb[UNROLL];
+            return is_finite(v) ? make_key(v, id0 + off) : 0ull;
+        };
+        // 32 list entries per thread between two votes (one `lost` bit each), four at a time so that their
+        // logit loads overlap
+        for (int j0 = 0; j0 < n_list; j0 += kThreads * 32) {
+            for (int g = 0; g < 8 && j0 + g * 4 * kThreads < n_list; ++g) {
+                int e[4];
+                float v[4];
+                bool ok[4];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int e = (v0 + u * kThreads + tid) * VEC;
-            mb[u] = e < n_s ? (eff[e >> 5] >> (e & 31)) & ((VEC == 32) ? 0xffffffffu : ((1u << VEC) - 1u)) : 0u;
-            if (mb[u]) {
-                if (VEC == 1 || e + VEC <= n_s) {
-                    load_vec<T, VEC>(x + e, xv[u]);
-                } else {  // the row's ragged end
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) xv[u][j] = e + j < n_s ? to_float(x[e + j]) : 0.0f;
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + (g * 4 + u) * kThreads + tid;
+                    e[u] = j < n_list ? htab[hlist[j]] : kHashEmpty;
+                    ok[u] = false;
+                    if (e[u] != kHashEmpty) {
+                        const uint32_t off = (uint32_t) e[u] >> 16;
+                        const uint32_t bit = 1u << (off & 31);
+                        ok[u] = (atomicAnd(&eff[off >> 5], ~bit) & bit) != 0u;  // allowed by the grammar mask
+                        if (ok[u]) v[u] = to_float(x[off]);
+                    }
                 }
-            }
-        }
-        if (k == 1) {
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                if (!mb[u]) continue;
-                const int e = (v0 + u * kThreads + tid) * VEC;
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) {
-                    const float xi = xv[u][j];
-                    if (((mb[u] >> j) & 1u) && xi >= best_v && xi <= FLT_MAX) {
-                        const uint64_t key = make_key(xi, id0 + (uint32_t) (e + j));
-                        if (key > best) { best = key; best_v = xi; }
+                for (int u = 0; u < 4; ++u) {
+                    if (!ok[u]) continue;
+                    const uint64_t key = entry_key(e[u], v[u]);
+                    if (key == 0ull) continue;
+                    if (k == 1) {
+                        best = key > best ? key : best;
+                    } else if (key >= *(volatile uint64_t *) &sh.thr_key && !push(key, buf, sh, a.cap)) {
+                        lost |= 1u << (g * 4 + u);
                     }
                 }
             }
-            continue;
-        }
-        const float thr_v = *(volatile float *) &sh.thr_value;
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            uint32_t pass = 0u;
-            if (mb[u]) {
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) pass |= (xv[u][j] >= thr_v ? 1u : 0u) << j;
-                pass &= mb[u];
-            }
-            if (!__any_sync(kFull, pass != 0u)) continue;
-            const uint64_t thr_key = *(volatile uint64_t *) &sh.thr_key;
-            const int e = (v0 + u * kThreads + tid) * VEC;
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-                uint64_t key = 0ull;
-                bool take = (pass >> j) & 1u;
-                if (take) {
-                    const float xi = xv[u][j];
-                    key = make_key(xi, id0 + (uint32_t) (e + j));
-                    take = xi <= FLT_MAX && key >= thr_key;  // +inf is never a candidate
-                }
-                const uint32_t ballot = __ballot_sync(kFull, take);
-                if (ballot) {
-                    uint32_t base = 0u;
-                    const int leader = __ffs(ballot) - 1;
-                    if (lane == leader) base = atomicAdd(&sh.n_cand, (uint32_t) __popc(ballot));
-                    base = __shfl_sync(kFull, base, leader);
-                    if (take) {
-                        const uint32_t pos = base + (uint32_t) __popc(ballot & ((1u << lane) - 1u));
-                        if (pos < (uint32_t) a.cap) buf[pos] = key;
-                        else atomicExch(a.err, 1);
+            if (k > 1) {
+                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                    compact(buf, sel, k, a.cap, sh);
+                    const uint64_t thr_key = sh.thr_key;
+                    uint32_t still = 0u;
+                    for (uint32_t m = lost; m; m &= m - 1u) {
+                        const int b = __ffs(m) - 1;
+                        const int e = htab[hlist[j0 + b * kThreads + tid]];
+                        const uint64_t key = entry_key(e, to_float(x[(uint32_t) e >> 16]));
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
                     }
+                    lost = still;
+                    if (!__syncthreads_or(lost != 0u)) break;
                 }
             }
         }
     }
     __syncthreads();
+    // The row's ragged end: the elements of a last, partial vector are taken here one by one and removed from
+    // the bit set, so that the vector loads below never reach past the row.
+    if (VEC > 1 && (n_s % VEC) != 0) {
+        if (tid < (n_s % VEC)) {
+            const int e = n_s - (n_s % VEC) + tid;
+            const uint32_t bit = 1u << (e & 31);
+            if (atomicAnd(&eff[e >> 5], ~bit) & bit) {
+                const float xi = to_float(x[e]);
+                if (is_finite(xi)) {
+                    const uint64_t key = make_key(xi, id0 + (uint32_t) e);
+                    if (k == 1) {
+                        best = key > best ? key : best;
+                    } else if (!push(key, buf, sh, a.cap)) {
+                        atomicExch(a.err, 1);  // cannot happen: at most VEC - 1 keys after a vote that left room
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    FNS_PHASE(1)
+
+    // 3. Pass 1 over the slice: maxima only.  An epoch gives every thread NV vectors (16 elements); two epochs
+    // are in flight (the loads of the next one are issued before the current one is reduced); a vector whose
+    // elements the bit set excludes is not loaded.  Nothing is appended here and no element is looked at
+    // individually: every thread keeps the maximum of what it has seen, and a 64-bit flag word marks the vector
+    // groups whose maximum reaches the running bound.  The bound needs no buffer: if r = ceil(k / warps) lanes
+    // of EVERY warp hold a maximum >= v, the slice has at least k elements >= v, so nothing below v can be among
+    // its best k.  Each warp finds its r-th largest lane maximum with r warp-wide max reductions and publishes
+    // it; the bound is the minimum over the warps (for k = 1: the maximum).  It is refreshed after epochs 1, 2,
+    // 4, 8, 16 and once more at the end.
+    const uint32_t * effp = eff + ((tid * VEC) >> 5);
+    const int bshift = (tid * VEC) & 31;
+    const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
+    const bool bounded = r_need <= 32;             // otherwise (k > 256) every group is flagged
+    float tmax = -INFINITY;                        // this thread's maximum so far
+    float thr_v = -FLT_MAX;                        // the bound as a float: x < thr_v cannot be a candidate
+    uint32_t thr_word = 0u;
+    uint64_t flags = 0ull;
+    int done = 0;
+
+    auto refresh = [&]() {  // all threads of the warp
+        uint32_t v = tmax > -INFINITY ? order_word(tmax) : 0u, bound = 0u;
+        int cnt = 0;
+        while (cnt < r_need) {
+            const uint32_t m = __reduce_max_sync(kFull, v);
+            if (m == 0u) { bound = 0u; break; }
+            cnt += __popc(__ballot_sync(kFull, v == m));
+            if (v == m) v = 0u;
+            bound = m;
+        }
+        if (lane == 0) *(volatile uint32_t *) &sh.warp_bound[warp] = bound;
+    };
+    auto read_bound = [&]() {
+        const volatile uint32_t * wb = sh.warp_bound;
+        uint32_t b = wb[0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) b = k == 1 ? max(b, wb[w]) : min(b, wb[w]);
+        if (b > thr_word) {
+            thr_word = b;
+            thr_v = word_value(b < 0x00800000u ? 0x00800000u : b);
+        }
+    };
+    auto issue = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            mb[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+            if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * kThreads * NV + i * kThreads + tid) * VEC), xv[i]);
+        }
+    };
+    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
+        float gm[FPE];
+#pragma unroll
+        for (int g = 0; g < FPE; ++g) {
+            gm[g] = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < VPF; ++u) {
+                const int i = g * VPF + u;
+                if (mb[i]) gm[g] = fmaxf(gm[g], vector_max<VEC>(xv[i], mb[i]));
+            }
+            tmax = fmaxf(tmax, gm[g]);
+        }
+        if (bounded && (done & (done + 1)) == 0) {  // done = 0, 1, 3, 7, 15
+            refresh();
+            if (done == 0) __syncthreads();  // the first bound needs every warp's share
+            read_bound();
+        }
+        ++done;
+#pragma unroll
+        for (int g = 0; g < FPE; ++g) flags |= (uint64_t) (gm[g] >= thr_v ? 1u : 0u) << (ep * FPE + g);
+    };
+    {
+        uint32_t todo = sh.epoch_mask;  // the same for every thread: read after the barrier above
+        auto next = [&]() -> int {
+            if (!todo) return -1;
+            const int ep = __ffs(todo) - 1;
+            todo &= todo - 1u;
+            return ep;
+        };
+        float xa[NV][VEC], xb[NV][VEC];
+        uint32_t ma[NV], mb[NV];
+        int ea = next(), eb = -1;
+        if (ea >= 0) issue(ea, xa, ma);
+        while (ea >= 0) {
+            eb = next();
+            if (eb >= 0) issue(eb, xb, mb);
+            reduce(ea, xa, ma);
+            if (eb < 0) break;
+            ea = next();
+            if (ea >= 0) issue(ea, xa, ma);
+            reduce(eb, xb, mb);
+        }
+    }
+    if (bounded && done > 1) {  // the final bound (after one epoch the first refresh already is)
+        refresh();
+        __syncthreads();
+        read_bound();
+    }
+    FNS_PHASE(2)
+
+    // Pass 2: only the flagged groups are read again (from L1 / L2: the slice was just streamed) and their
+    // elements compared with the final bound, one group per thread and round.  What passes is appended; the block
+    // votes once per round on whether to compact (buffer filling up, or an append that found it full, which is
+    // then offered again after the compaction).
+    if (k == 1) {
+        while (flags) {
+            const int b = __ffsll((long long) flags) - 1;
+            flags &= flags - 1ull;
+            const int ep = b / FPE, g = b - ep * FPE;
+#pragma unroll
+            for (int u = 0; u < VPF; ++u) {
+                const int i = g * VPF + u;
+                const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC;
+                const uint32_t bits = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+                if (!bits) continue;
+                float xv[VEC];
+                load_vec<T, VEC>(x + e, xv);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    if (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) {
+                        const uint64_t key = make_key(xv[j], id0 + (uint32_t) (e + j));
+                        best = key > best ? key : best;
+                    }
+                }
+            }
+        }
+    } else {
+        uint64_t thr_key = (uint64_t) thr_word << 32;
+        {
+            const uint64_t tk = sh.thr_key;  // a compaction of the penalty phase may have left a higher bar
+            if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+        }
+        while (__syncthreads_or(flags != 0ull)) {
+            int ep = 0, g = 0;
+            const bool has = flags != 0ull;
+            if (has) {
+                const int b = __ffsll((long long) flags) - 1;
+                flags &= flags - 1ull;
+                ep = b / FPE;
+                g = b - ep * FPE;
+#pragma unroll
+                for (int u = 0; u < VPF; ++u) {
+                    const int i = g * VPF + u;
+                    const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC;
+                    const uint32_t bits = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+                    if (!bits) continue;
+                    float xv[VEC];
+                    load_vec<T, VEC>(x + e, xv);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        if (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) {
+                            const uint64_t key = make_key(xv[j], id0 + (uint32_t) (e + j));
+                            if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (u * VEC + j);
+                        }
+                    }
+                }
+            }
+            while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                compact(buf, sel, k, a.cap, sh);
+                const uint64_t tk = sh.thr_key;
+                if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+                uint32_t still = 0u;
+                for (uint32_t m = lost; m; m &= m - 1u) {
+                    const int b = __ffs(m) - 1;
+                    const int i = g * VPF + b / VEC;
+                    const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC + (b % VEC);
+                    const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
+                    if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+                }
+                lost = still;
+                if (!__syncthreads_or(lost != 0u)) break;
+            }
+        }
+    }
+    __syncthreads();
+    FNS_PHASE(3)
 
     // 4. The slice's answer: its best k keys in the total order.
     if (k == 1) {
@@ -290,23 +665,74 @@ __global__ void __launch_bounds__(kThreads) k_select(const SelectArgs a) {
             const uint64_t other = __shfl_xor_sync(kFull, best, o);
             best = other > best ? other : best;
         }
-        if (lane == 0) sh.red[tid >> 5] = best;
+        if (lane == 0) sh.red[warp] = best;
         __syncthreads();
         if (tid == 0) {
             uint64_t b = sh.red[0];
-            for (int w = 1; w < kThreads / 32; ++w) b = sh.red[w] > b ? sh.red[w] : b;
+            for (int w = 1; w < kWarps; ++w) b = sh.red[w] > b ? sh.red[w] : b;
             out[0] = b;
         }
+    } else {
+        const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
+        const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
+        const int got = block_take(buf, n, k, tau, sel, sh.sc);
+        block_rank_sort(sel, got, out);
+        for (int j = got + tid; j < k; j += kThreads) out[j] = 0ull;
+    }
+    FNS_PHASE(4)
+    if (!a.tickets) return;
+
+    // 5. The last block of the row to get here merges the slices' lists and draws.  Nobody waits: every block
+    // takes a ticket after its list is visible, and the one that draws the last ticket does the work.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned t = atomicAdd(&a.tickets[row], 1u);
+        sh.is_last = t == (unsigned) a.slices - 1u;
+        if (sh.is_last) a.tickets[row] = 0u;  // ready for the next launch
+        sh.n_keys = 0u;
+    }
+    __syncthreads();
+    if (!sh.is_last) return;
+    __threadfence();
+    const uint64_t * lists = a.cand + (size_t) row * a.slices * a.k_cap;
+    p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
+    if (k == 1) {  // greedy: the largest of the slices' best keys, no sort, no draw
+        uint64_t b = 0ull;
+        for (int l = tid; l < a.slices; l += kThreads) {
+            const uint64_t key = __ldcg(lists + (size_t) l * a.k_cap);
+            b = key > b ? key : b;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const uint64_t other = __shfl_xor_sync(kFull, b, o);
+            b = other > b ? other : b;
+        }
+        if (lane == 0) sh.red[warp] = b;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < kWarps; ++w) b = sh.red[w] > b ? sh.red[w] : b;
+            if (a.out_tokens) a.out_tokens[row] = b ? key_id(b) : -1;
+            if (a.out_cands) a.out_cands[(size_t) row * a.k_cap] = key_to_cand(b);
+        }
+        if (a.out_cands)
+            for (int j = 1 + tid; j < a.k_cap; j += kThreads) a.out_cands[(size_t) row * a.k_cap + j] = key_to_cand(0ull);
+        FNS_PHASE(5)
         return;
     }
-    const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
-    const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
-    const int got = block_take(buf, n, k, tau, sel, sh.sc);
-    block_rank_sort(sel, got, out);
-    for (int j = got + tid; j < k; j += kThreads) out[j] = 0ull;
+    // the slices' lists, each sorted, side by side in the buffer: [slices][k]
+    for (int i = tid; i < a.slices * k; i += kThreads) {
+        const int l = i / k, j = i - l * k;
+        buf[i] = __ldcg(lists + (size_t) l * a.k_cap + j);
+    }
+    __syncthreads();
+    finalize_row(buf, a.slices, k, sel, sorted, pj, acc, sh.sc, sh.keep, p, k, a.k_cap,
+                 a.out_tokens ? a.out_tokens + row : nullptr,
+                 a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
+    FNS_PHASE(5)
 }
 
-// ---- finalize ---------------------------------------------------------------------------------------------
+// ---- finalize as a kernel of its own -------------------------------------------------------------------------
 struct FinalArgs {
     const uint64_t * keys;        // internal lists (sorted keys, 0 = empty), or
     const fns_b200_cand * cands;  // external lists; entry j of list l of row r at r * row_stride + l * list_stride + j
@@ -325,7 +751,6 @@ struct FinalArgs {
 struct FinalShared {
     SelectScratch sc;
     uint32_t n_keys;
-    int nk;
     int keep;
 };
 
@@ -335,96 +760,29 @@ __global__ void __launch_bounds__(kThreads) k_finalize(const FinalArgs a) {
     const int row = blockIdx.x;
     const int W = a.n_draft + 1, win = row / W, col = row - win * W;
     fns_b200_params p = a.params ? a.params[win] : a.p0;
-    p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
-    const bool greedy = p.temperature <= 0.0f;
-    const int k = greedy ? 1 : clamp_k(p.top_k, a.k_cap);
+    p.counter += (uint64_t) col;
+    const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
     const int take_len = a.keys ? min(a.list_len, k) : a.list_len;  // internal lists hold exactly the row's k
 
     // shared memory: all keys of the row | selection staging | sorted result | p / acc (fp64)
-    const int max_keys = a.lists * a.list_len;
     uint64_t * buf = reinterpret_cast<uint64_t *>(smem_raw);
-    uint64_t * sel = buf + max_keys;
+    uint64_t * sel = buf + a.lists * a.list_len;
     uint64_t * sorted = sel + a.k_cap;
     double * pj = reinterpret_cast<double *>(sorted + a.k_cap);
     double * acc = pj + a.k_cap;
     FinalShared & sh = *reinterpret_cast<FinalShared *>(acc + a.k_cap);
 
-    if (tid == 0) {
-        sh.n_keys = 0u;
-        sh.nk = 0;
-        sh.keep = 0;
-    }
-    for (int j = tid; j < a.k_cap; j += kThreads) sorted[j] = 0ull;
-    __syncthreads();
-    // Gather the non-empty keys (their order does not matter: the selection below is by key alone, which makes
-    // the result independent of how many slices or shards produced the lists).
+    // the row's lists side by side: [lists][take_len]
     const size_t row_base = (size_t) row * a.row_stride;
     for (int i = tid; i < a.lists * take_len; i += kThreads) {
         const int l = i / take_len, j = i - l * take_len;
         const size_t at = row_base + (size_t) l * a.list_stride + j;
-        const uint64_t key = a.keys ? a.keys[at] : cand_to_key(a.cands[at]);
-        if (key != 0ull) buf[atomicAdd(&sh.n_keys, 1u)] = key;
+        buf[i] = a.keys ? a.keys[at] : cand_to_key(a.cands[at]);
     }
     __syncthreads();
-    const int n = (int) sh.n_keys;
-    const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
-    const int got = block_take(buf, n, k, tau, sel, sh.sc);
-    block_rank_sort(sel, got, sorted);
-    __syncthreads();
-    const int nk = got;  // number of candidates (fewer than k allowed tokens: src/kernels.cu:698-699)
-    if (a.out_cands)
-        for (int j = tid; j < a.k_cap; j += kThreads) a.out_cands[(size_t) row * a.k_cap + j] = key_to_cand(sorted[j]);
-    if (!a.out_tokens) return;
-    if (nk == 0) {
-        if (tid == 0) a.out_tokens[row] = -1;
-        return;
-    }
-    if (greedy || nk == 1) {
-        if (tid == 0) a.out_tokens[row] = key_id(sorted[0]);
-        return;
-    }
-    // k_sample's tail (src/kernels.cu:702-719).  exp and the quotients are per-element and computed in parallel;
-    // the three running sums keep the reference's left-to-right order, one chain per thread: `sum` then `cum`
-    // on thread 0, the weight prefix (which is both wsum and the inverse-CDF walk's acc) on thread 32.
-    const double v0 = (double) key_value(sorted[0]);
-    for (int j = tid; j < nk; j += kThreads) {
-        const double d = (double) key_value(sorted[j]) - v0;
-        pj[j] = exp(d);
-        acc[j] = exp(d / p.temperature);
-    }
-    __syncthreads();
-    if (tid == 0) {
-        double sum = 0.0;
-        for (int j = 0; j < nk; ++j) sum += pj[j];
-        int keep = nk;
-        double cum = 0.0;
-        for (int j = 0; j < nk; ++j) {
-            cum += pj[j] / sum;
-            if (cum >= p.top_p) { keep = j + 1; break; }
-        }
-        if (p.min_p > 0.0f) {
-            int m = 1;
-            while (m < keep && pj[m] >= (double) p.min_p) ++m;
-            keep = m;
-        }
-        sh.keep = keep;
-    } else if (tid == 32) {
-        double run = 0.0;
-        for (int j = 0; j < nk; ++j) {
-            run += acc[j];
-            acc[j] = run;
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        const int keep = sh.keep;
-        const double wsum = acc[keep - 1];
-        const double u = philox_uniform(p.seed, p.counter) * wsum;
-        int pick = keep - 1;
-        for (int j = 0; j < keep; ++j)
-            if (u < acc[j]) { pick = j; break; }
-        a.out_tokens[row] = key_id(sorted[pick]);
-    }
+    finalize_row(buf, a.lists, take_len, sel, sorted, pj, acc, sh.sc, sh.keep, p, k, a.k_cap,
+                 a.out_tokens ? a.out_tokens + row : nullptr,
+                 a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
 }
 
 // a = number of leading columns whose token equals the draft (tools/fns_serve/fns_serve.cpp:492-508).
@@ -470,8 +828,9 @@ struct fns_b200_sampler {
     int max_rows, max_vocab, k_cap, max_history;
     int sm_count;
     int force_slices;
-    uint64_t * cand;   // [max_rows][kMaxSlices or fewer][k_cap]
+    uint64_t * cand;   // [rows][slices][k_cap] sorted keys of the slices
     size_t cand_entries;
+    unsigned * tickets;  // [max_rows], zero between launches
     int * err;
     int64_t launches;
     bool prof_on;
@@ -483,8 +842,9 @@ struct fns_b200_sampler {
 namespace {
 
 struct Plan {
-    int slices, slice_len, cap, high_water, ht_size, vec, unroll;
-    size_t smem_select, smem_final;
+    int slices, slice_len, cap, trigger, ht_size, vec;
+    bool fused;  // the last block of a row merges and draws inside k_select
+    size_t smem_select;
 };
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -503,17 +863,20 @@ int fail_cuda(fns_b200_sampler * s, cudaError_t e, const char * where) {
     return FNS_B200_ERR_CUDA;
 }
 
-// Launch geometry.  Slices per row: enough blocks to fill the GPU (about four 256-thread blocks per SM) when
-// rows are few, long slices when rows are many (the per-slice selection cost is amortised over the stream).
+// Launch geometry.  Slices per row: about twelve 256-thread blocks per SM over the whole call, so that the
+// hardware block scheduler evens out rows whose masks make them cheap or expensive; no slice shorter than 2048
+// elements; the slices' lists of one row must fit the merge (kMaxMergeKeys) and, for the fused finalize, the
+// candidate buffer of the block that does it.
 bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
     const int k_cap = s->k_cap;
     const int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
     int max_slices = kMaxMergeKeys / k_cap;
     if (max_slices > kMaxSlices) max_slices = kMaxSlices;
     if (min_slices > max_slices) return false;
-    int want = s->force_slices > 0 ? s->force_slices : (s->sm_count * 4 + rows - 1) / rows;
-    const int by_len = (vocab + 2 * kSliceAlign - 1) / (2 * kSliceAlign);  // no slice shorter than 2048 elements
+    int want = s->force_slices > 0 ? s->force_slices : (s->sm_count * 12 + rows - 1) / rows;
+    const int by_len = (vocab + kSliceAlign - 1) / kSliceAlign;  // no slice shorter than one epoch
     if (s->force_slices <= 0 && want > by_len) want = by_len;
+    if (s->force_slices <= 0 && want > 64) want = 64;
     if (want < min_slices) want = min_slices;
     if (want > max_slices) want = max_slices;
     if (want < 1) want = 1;
@@ -521,17 +884,18 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     if (pl.slice_len > kMaxSliceLen) pl.slice_len = kMaxSliceLen;
     pl.slices = (vocab + pl.slice_len - 1) / pl.slice_len;
     pl.vec = aligned ? (dtype == FNS_B200_BF16 ? 8 : 4) : 1;
-    pl.unroll = 2;
-    const int tile = kThreads * pl.unroll * pl.vec;
-    pl.high_water = 3 * k_cap > 1024 ? 3 * k_cap : 1024;
-    pl.cap = pl.high_water + (tile > kThreads ? tile : kThreads);
+    const int base_cap = 4 * k_cap > 2048 ? 4 * k_cap : 2048;
+    pl.trigger = base_cap / 2;
+    pl.cap = base_cap;
+    pl.fused = true;
+    if (pl.slices * k_cap > pl.cap) pl.cap = pl.slices * k_cap;  // room to merge the row's lists
     pl.ht_size = 0;
     if (hist_bound > 0) {
         const int distinct = hist_bound < pl.slice_len ? hist_bound : pl.slice_len;
         pl.ht_size = next_pow2(2 * distinct);
         if (pl.ht_size < kThreads) pl.ht_size = kThreads;
     }
-    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 + (size_t) pl.slice_len / 8 + (size_t) pl.ht_size * 4 +
+    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.ht_size * 6 +
                      sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
@@ -542,7 +906,7 @@ size_t final_smem(int lists, int list_len, int k_cap) {
 
 template <typename T, int VEC>
 cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
-    auto kern = k_select<T, VEC, 2>;
+    auto kern = k_select<T, VEC>;
     static bool configured[64] = {};  // per device: the opt-in to large dynamic shared memory is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -592,7 +956,8 @@ struct DeviceGuard {
 int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
                int32_t id_base, const uint32_t * masks, int64_t mask_stride, const int32_t * history,
                int64_t history_stride, const int32_t * history_len, const int32_t * draft, int n_draft,
-               const fns_b200_params * params, const fns_b200_params * p0, cudaStream_t st, Plan & pl) {
+               const fns_b200_params * params, const fns_b200_params * p0, int32_t * out_tokens,
+               fns_b200_cand * out_cands, cudaStream_t st, Plan & pl) {
     if (!s) return FNS_B200_ERR_ARG;
     if (!logits || rows <= 0 || vocab <= 0) return fail(s, FNS_B200_ERR_ARG, "logits null, or rows / vocab <= 0");
     if (dtype != FNS_B200_F32 && dtype != FNS_B200_BF16) return fail(s, FNS_B200_ERR_ARG, "dtype must be F32 or BF16");
@@ -629,21 +994,31 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.slices = pl.slices;
     a.slice_len = pl.slice_len;
     a.cap = pl.cap;
-    a.high_water = pl.high_water;
+    a.trigger = pl.trigger;
     a.ht_size = pl.ht_size;
     a.cand = s->cand;
+    a.tickets = pl.fused ? s->tickets : nullptr;
+    a.out_tokens = out_tokens;
+    a.out_cands = out_cands;
     a.err = s->err;
     const bool prof = s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size();
     if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3], st);
     const cudaError_t e = launch_select(a, dtype, pl.vec, rows, pl.smem_select, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "select launch");
-    if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 1], st);
     ++s->launches;
+    if (prof) {
+        cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 1], st);
+        if (pl.fused) {  // no finalize launch follows: close the record here
+            cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 2], st);
+            ++s->prof_calls;
+        }
+    }
     return FNS_B200_OK;
 }
 
 int run_final_internal(fns_b200_sampler * s, const Plan & pl, int rows, int n_draft, const fns_b200_params * params,
                        const fns_b200_params * p0, int32_t * out_tokens, fns_b200_cand * out_cands, cudaStream_t st) {
+    if (pl.fused) return FNS_B200_OK;  // k_select already merged and drew
     FinalArgs f{};
     f.keys = s->cand;
     f.lists = pl.slices;
@@ -705,9 +1080,12 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
     const size_t cap_entries = (size_t) 1 << 27;  // 1 GiB of keys at most
     if (s->cand_entries > cap_entries) s->cand_entries = cap_entries;
     if (cudaMalloc(&s->cand, s->cand_entries * sizeof(uint64_t)) != cudaSuccess ||
-        cudaMalloc(&s->err, sizeof(int)) != cudaSuccess || cudaMemset(s->err, 0, sizeof(int)) != cudaSuccess) {
+        cudaMalloc(&s->err, sizeof(int)) != cudaSuccess || cudaMemset(s->err, 0, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&s->tickets, (size_t) max_rows * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(s->tickets, 0, (size_t) max_rows * sizeof(unsigned)) != cudaSuccess) {
         if (s->cand) cudaFree(s->cand);
         if (s->err) cudaFree(s->err);
+        if (s->tickets) cudaFree(s->tickets);
         delete s;
         return FNS_B200_ERR_CUDA;
     }
@@ -720,6 +1098,7 @@ int fns_b200_destroy(fns_b200_sampler * s) {
     DeviceGuard g(s->device);
     cudaFree(s->cand);
     cudaFree(s->err);
+    cudaFree(s->tickets);
     for (cudaEvent_t ev : s->prof_ev) cudaEventDestroy(ev);
     delete s;
     return FNS_B200_OK;
@@ -799,7 +1178,7 @@ int fns_b200_sample_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     DeviceGuard g(s->device);
     Plan pl;
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
-                        history_len, nullptr, 0, params, nullptr, (cudaStream_t) stream, pl);
+                        history_len, nullptr, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
     return run_final_internal(s, pl, rows, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream);
 }
@@ -813,7 +1192,7 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
     DeviceGuard g(s->device);
     Plan pl;
     int rc = run_select(s, logits, dtype, vocab, vocab, 1, 0, mask, (vocab + 31) / 32, nullptr, 0, nullptr, nullptr, 0,
-                        nullptr, params_host, (cudaStream_t) stream, pl);
+                        nullptr, params_host, out_token, nullptr, (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
     return run_final_internal(s, pl, 1, 0, nullptr, params_host, out_token, nullptr, (cudaStream_t) stream);
 }
@@ -827,7 +1206,8 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     DeviceGuard g(s->device);
     Plan pl;
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, id_base, masks, mask_stride_words, history,
-                        history_stride, history_len, nullptr, 0, params, nullptr, (cudaStream_t) stream, pl);
+                        history_stride, history_len, nullptr, 0, params, nullptr, nullptr, out_cands,
+                        (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
     return run_final_internal(s, pl, rows, 0, params, nullptr, nullptr, out_cands, (cudaStream_t) stream);
 }
@@ -869,7 +1249,7 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
     const int rows = windows * (n_draft + 1);
     Plan pl;
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
-                        history_len, draft, n_draft, params, nullptr, (cudaStream_t) stream, pl);
+                        history_len, draft, n_draft, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
     rc = run_final_internal(s, pl, rows, n_draft, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream);
     if (rc != FNS_B200_OK) return rc;
@@ -880,6 +1260,17 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
     ++s->launches;
     return FNS_B200_OK;
 }
+
+#ifdef FNS_PHASE_TIMING
+// development aid (not part of the ABI header): reads and clears the phase clocks
+int fns_b200_debug_phases(unsigned long long * out8) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 8);
+    unsigned long long zero[8] = {};
+    cudaMemcpyToSymbol(fnsb::g_phase, zero, sizeof zero);
+    return 0;
+}
+#endif
 
 int fns_b200_presence_apply(float * x, const float * seen, int n, float penalty, void * stream) {
     if (!x || !seen || n <= 0) return FNS_B200_ERR_ARG;
