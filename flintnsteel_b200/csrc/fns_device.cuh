@@ -13,7 +13,6 @@
 namespace fnsb {
 
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kThreads = 256;  // every kernel of the sampler runs 256-thread blocks
 
 // ---- keys ---------------------------------------------------------------------------------------------
 // The reference orders candidates by value descending, then index ascending, with float compares
@@ -90,7 +89,8 @@ struct SelectScratch {
 // MSB-first radix select, 8 bits per pass, starting below the bits that all keys share (the keys that reach a
 // compaction lie in a narrow value range, so their leading bits agree and a histogram over them would put
 // every atomic on one bin).  It stops as soon as the pivot bucket is taken whole; tau then has zero low bits.
-// Called by all kThreads threads with uniform arguments; ends with the block synchronised.
+// Called by all NT threads of the block with uniform arguments; ends with the block synchronised.
+template <int NT>
 __device__ uint64_t block_kth_key(const uint64_t * buf, int n, int k, SelectScratch & sc) {
     const int tid = threadIdx.x, lane = tid & 31;
     if (n <= k) return 0ull;
@@ -101,7 +101,7 @@ __device__ uint64_t block_kth_key(const uint64_t * buf, int n, int k, SelectScra
     __syncthreads();
     {
         uint32_t oh = 0, ol = 0, ah = 0xffffffffu, al = 0xffffffffu;
-        for (int i = tid; i < n; i += kThreads) {
+        for (int i = tid; i < n; i += NT) {
             const uint64_t key = buf[i];
             oh |= (uint32_t) (key >> 32);
             ol |= (uint32_t) key;
@@ -131,9 +131,9 @@ __device__ uint64_t block_kth_key(const uint64_t * buf, int n, int k, SelectScra
         const int bits = remaining < 8 ? remaining : 8;
         const int shift = remaining - bits;
         const uint32_t dmask = (1u << bits) - 1u;
-        sc.hist[tid] = 0u;
+        for (int i = tid; i < 256; i += NT) sc.hist[i] = 0u;
         __syncthreads();
-        for (int i = tid; i < n; i += kThreads) {
+        for (int i = tid; i < n; i += NT) {
             const uint64_t key = buf[i];
             if ((key & pmask) == prefix) atomicAdd(&sc.hist[(uint32_t) (key >> shift) & dmask], 1u);
         }
@@ -182,11 +182,12 @@ __device__ uint64_t block_kth_key(const uint64_t * buf, int n, int k, SelectScra
 
 // Moves the keys >= tau of buf[0 .. n) (at most k of them) to sel[0 .. ), and returns how many.  sc.count is the
 // cursor.  Ends with the block synchronised.
+template <int NT>
 __device__ int block_take(const uint64_t * buf, int n, int k, uint64_t tau, uint64_t * sel, SelectScratch & sc) {
     const int tid = threadIdx.x;
     if (tid == 0) sc.count = 0u;
     __syncthreads();
-    for (int i = tid; i < n; i += kThreads) {
+    for (int i = tid; i < n; i += NT) {
         const uint64_t key = buf[i];
         if (key >= tau) {
             const uint32_t pos = atomicAdd(&sc.count, 1u);
@@ -201,13 +202,28 @@ __device__ int block_take(const uint64_t * buf, int n, int k, uint64_t tau, uint
 
 // out[rank] = key for the m distinct keys of sel, rank = number of larger keys: descending order = the total
 // order.  out may be shared or global.  No synchronisation inside.
+template <int NT>
 __device__ void block_rank_sort(const uint64_t * sel, int m, uint64_t * out) {
-    for (int i = threadIdx.x; i < m; i += kThreads) {
+    for (int i = threadIdx.x; i < m; i += NT) {
         const uint64_t key = sel[i];
         int rank = 0;
         for (int j = 0; j < m; ++j) rank += sel[j] > key ? 1 : 0;
         out[rank] = key;
     }
+}
+
+// For small n: out[rank] = key for every key whose rank (number of larger keys) is below k: the best k in the
+// total order, with no barrier and no scratch.  Every key is compared with every other, so only worth it while
+// n * n / NT stays small.  Returns min(n, k); out must not alias buf.
+template <int NT>
+__device__ int block_rank_select(const uint64_t * buf, int n, int k, uint64_t * out) {
+    for (int i = threadIdx.x; i < n; i += NT) {
+        const uint64_t key = buf[i];
+        int rank = 0;
+        for (int j = 0; j < n; ++j) rank += buf[j] > key ? 1 : 0;
+        if (rank < k) out[rank] = key;
+    }
+    return n < k ? n : k;
 }
 
 }  // namespace fnsb

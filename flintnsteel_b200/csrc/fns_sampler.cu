@@ -2,21 +2,32 @@
 //
 // HBM-streaming / latency work with no contraction in it (no tensor cores):
 //
-//   k_select   grid (slices, rows).  One pass over a slice of one row of logits: 128-bit coalesced loads, the
-//              grammar bitmask and the penalty history folded into a shared-memory bit set, and an exact
-//              top-k of the slice by threshold filtering: elements that beat the current k-th best key are
-//              appended to a shared buffer; when the buffer fills, the block radix-selects the best k and
-//              raises the threshold.  Regions that the bit set masks out are skipped without touching the
-//              logits.  Replaces k_topk_part of the reference (src/kernels.cu:624-648), which rescans its slice
-//              k times, and k_presence_apply / _col (src/kernels.cu:724-742), which rewrite the whole row.
-//              The last block of a row to finish (a ticket, no waiting) merges the slices' candidates and
-//              draws the token, so a whole call is ONE launch.
-//   k_finalize grid (rows).  The same merge + draw as a kernel of its own, for candidate lists that come from
-//              elsewhere (vocabulary shards gathered from other GPUs): k_sample of the reference
-//              (src/kernels.cu:671-721).
+//   k_select   grid (slices, rows); one block per (row, slice).  With many rows a slice is the whole row and a
+//              block has 512 threads (two per SM: 296 rows in flight at once); with few rows a row is cut into
+//              slices of 256-thread blocks so that the whole GPU works on it.  Per slice:
+//                1. the grammar bitmask and the penalty history are folded into a shared-memory bit set;
+//                2. pass 1 streams the logits once with 128-bit coalesced loads, two epochs in flight, and keeps
+//                   nothing but maxima: per thread the maximum seen, per vector group one flag "reaches the
+//                   running bound".  The bound is a value that at least k elements of the slice are known to
+//                   reach, found with warp-wide max reductions over the threads' maxima; nothing is appended,
+//                   nothing is compared element by element, regions the bit set masks out are never loaded;
+//                3. pass 2 reads the flagged groups again (L2) and appends the elements that reach the final
+//                   bound (about k to 2k of them) to a shared buffer; penalised candidates join them;
+//                4. the best k of the buffer, sorted, are the slice's answer (rank by counting, or radix select
+//                   when an adversarial input has filled the buffer; the buffer is compacted whenever it fills,
+//                   so any input is handled exactly);
+//                5. the last block of a row to finish (a ticket, no waiting) merges the slices' lists and does
+//                   the candidate softmax, top-p / min-p cut, temperature weights and Philox draw.
+//              Replaces k_topk_part (src/kernels.cu:624-648, which rescans its slice k times), k_presence_apply /
+//              _col (src/kernels.cu:724-742, which rewrite the whole row) and k_sample (src/kernels.cu:671-721)
+//              of the reference: a whole call is ONE launch.
+//   k_finalize grid (rows).  The merge + draw as a kernel of its own, for candidate lists that come from
+//              elsewhere (vocabulary shards gathered from other GPUs).
 //
 // Nothing here waits on another block, so there is no spin loop anywhere in the sampler.
 #include "fns_device.cuh"
+
+#include <cooperative_groups.h>
 
 #include <cstdio>
 #include <cstring>
@@ -26,7 +37,7 @@
 namespace fnsb {
 
 #ifdef FNS_PHASE_TIMING  // development aid: block time per phase, summed over blocks (thread 0's clock)
-__device__ unsigned long long g_phase[8];
+__device__ unsigned long long g_phase[16];
 #define FNS_PHASE_BEGIN long long ph_t = clock64();
 #define FNS_PHASE(i)                                                           \
     if (threadIdx.x == 0) {                                                    \
@@ -34,17 +45,20 @@ __device__ unsigned long long g_phase[8];
         atomicAdd(&g_phase[i], (unsigned long long) (ph_n - ph_t));            \
         ph_t = ph_n;                                                           \
     }
+#define FNS_MARK(i) __syncthreads(); FNS_PHASE(i)
 #else
 #define FNS_PHASE_BEGIN
 #define FNS_PHASE(i)
+#define FNS_MARK(i)
 #endif
 
-constexpr int kHashEmpty = -1;             // 0xffffffff
-constexpr int kMaxMergeKeys = 8192;        // k_finalize holds the lists of one row in shared memory
+constexpr int kHashEmpty = -1;
+constexpr int kMaxMergeKeys = 8192;   // k_finalize holds the lists of one row in shared memory
 constexpr int kMaxSlices = 128;
-constexpr int kMaxSliceLen = 65536;        // a history table entry keeps the in-slice offset in 16 bits
-constexpr int kSliceAlign = 4096;          // slice length granularity (elements): one epoch of a block
-constexpr int kEpochElems = 16;            // elements per thread between two block votes
+constexpr int kEpochElems = 16;       // elements per thread and epoch
+// epochs per slice: at most 16 for 256-thread blocks and 32 for 512-thread blocks (64 flag bits per thread)
+constexpr int kMaxWarps = 16;
+constexpr int kRankSelectMax = 384;   // candidate sets up to this size are ranked by counting
 
 struct SelectArgs {
     const void * logits;
@@ -62,47 +76,48 @@ struct SelectArgs {
     fns_b200_params p0;
     int k_cap;
     int slices;
-    int slice_len;
+    int slice_len;   // a multiple of the block's epoch
     int cap;         // candidate buffer entries (>= 4 * k_cap)
-    int trigger;     // compact when the buffer holds this many, to keep the threshold fresh
-    int ht_size;     // history table slots (power of two, multiple of kThreads), 0: no table
+    int trigger;     // compact when the buffer holds this many
+    int ht_size;     // history table slots (power of two >= 1024), 0: no table
+    int ht_shift;    // 32 - log2(ht_size): the table index is the high bits of a multiplicative hash
+    int stash_cap;   // entries of the flagged-vector stash
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
-    unsigned * tickets;         // [rows], zero between launches; null: no fused finalize
-    int32_t * out_tokens;       // fused finalize: [rows], may be null
-    fns_b200_cand * out_cands;  // fused finalize: [rows][k_cap], may be null
+    unsigned * tickets;         // [rows], zero between launches
+    int32_t * out_tokens;       // [rows], may be null
+    fns_b200_cand * out_cands;  // [rows][k_cap], may be null
     int * err;
 };
 
 struct SelectShared {
     SelectScratch sc;
-    uint64_t thr_key;   // keys below this cannot be among the slice's best k
-    float thr_value;    // x < thr_value  =>  key < thr_key
-    uint32_t n_cand;    // append cursor; may run past cap (the excess was not stored: see `lost`)
-    uint32_t n_keys;
-    int keep;
-    int is_last;
+    uint64_t thr_key;     // the exact k-th best key of the buffer at its last compaction
+    uint32_t n_cand;      // append cursor; may run past cap (the excess was not stored: see `lost`)
     uint32_t epoch_mask;  // epochs of the slice that have an allowed element
     uint32_t n_list;      // occupied slots of the history table
-    __align__(16) uint32_t warp_bound[kThreads / 32];  // per warp: a value that r of its lanes have reached
-    uint64_t red[kThreads / 32];
+    uint32_t n_stash;     // flagged groups kept in shared memory for pass 2
+    int keep;
+    int is_last;
+    __align__(16) uint32_t warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
+    uint64_t red[kMaxWarps];
 };
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// 16-byte load of VEC consecutive elements, widened to fp32.  Streaming: each logit is read once.
+// 16-byte load of VEC consecutive elements, widened to fp32.
 template <typename T, int VEC>
 __device__ __forceinline__ void load_vec(const T * p, float (&out)[VEC]) {
     if constexpr (VEC == 1) {
         out[0] = to_float(*p);
     } else if constexpr (sizeof(T) == 4) {
-        const float4 v = __ldcs(reinterpret_cast<const float4 *>(p));
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
         out[0] = v.x;
         out[1] = v.y;
         out[2] = v.z;
         out[3] = v.w;
     } else {
-        const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(p));
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -113,9 +128,13 @@ __device__ __forceinline__ void load_vec(const T * p, float (&out)[VEC]) {
 }
 
 // One key into the candidate buffer.  False when the buffer is full: the caller remembers the element and
-// offers it again after the next compaction.
+// offers it again after the next compaction.  One reservation serves all the lanes that are here together:
+// atomics on one shared word serialise.
 __device__ __forceinline__ bool push(uint64_t key, uint64_t * buf, SelectShared & sh, int cap) {
-    const uint32_t pos = atomicAdd(&sh.n_cand, 1u);
+    const cooperative_groups::coalesced_group g = cooperative_groups::coalesced_threads();
+    uint32_t base = 0u;
+    if (g.thread_rank() == 0) base = atomicAdd(&sh.n_cand, g.size());
+    const uint32_t pos = g.shfl(base, 0) + g.thread_rank();
     if (pos < (uint32_t) cap) {
         buf[pos] = key;
         return true;
@@ -123,42 +142,40 @@ __device__ __forceinline__ bool push(uint64_t key, uint64_t * buf, SelectShared 
     return false;
 }
 
-// Keeps the best k keys of the buffer in buf[0 .. k) and raises the threshold.  All threads; the block is
-// synchronised on entry (every append is visible) and on exit.
+// Keeps the best k keys of the buffer in buf[0 .. k) and records the k-th as the new bar.  All threads; the
+// block is synchronised on entry (every append is visible) and on exit.
+template <int NT>
 __device__ void compact(uint64_t * buf, uint64_t * sel, int k, int cap, SelectShared & sh) {
     const int n = (int) min(sh.n_cand, (uint32_t) cap);
     if (n <= k) return;
-    const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
-    const int got = block_take(buf, n, k, tau, sel, sh.sc);
-    for (int i = threadIdx.x; i < got; i += kThreads) buf[i] = sel[i];
+    const uint64_t tau = block_kth_key<NT>(buf, n, k, sh.sc);
+    const int got = block_take<NT>(buf, n, k, tau, sel, sh.sc);
+    for (int i = threadIdx.x; i < got; i += NT) buf[i] = sel[i];
     if (threadIdx.x == 0) {
         sh.n_cand = (uint32_t) got;
         sh.thr_key = tau;
-        sh.thr_value = key_floor_value(tau);
     }
     __syncthreads();
 }
 
-// The candidate softmax, top-p / min-p cut, temperature weights and Philox draw of k_sample
-// (src/kernels.cu:698-720) for one row.  buf holds `lists` lists of `len` keys each, every list sorted in the
-// total order with its empty slots (0) at the end; they are first merged into the best k, sorted (the selection
-// rounds of src/kernels.cu:680-695): with few lists by ranking every key (its position plus, by binary search,
-// the number of larger keys in each other list; no barrier), else by radix selection.  All kThreads threads,
-// block synchronised on entry.  p.counter is the counter of this row.  exp and the quotients are per-element and
-// run in parallel; the three running sums keep the reference's left-to-right order: `sum` then `cum` on thread
-// 0, the weight prefix (which is both wsum and the acc of the inverse-CDF walk) on thread 32.
-__device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel, uint64_t * sorted, double * pj,
-                             double * acc, SelectScratch & sc, int & sh_keep, const fns_b200_params & p, int k,
-                             int k_cap, int32_t * out_token, fns_b200_cand * out_cands) {
+// `lists` lists of `len` keys each in buf, every list sorted in the total order with its empty slots (0) at the
+// end, merged into sorted[0 .. k): the selection rounds of k_sample (src/kernels.cu:680-695).  With few lists
+// every key is ranked directly (its position plus, by binary search, the number of larger keys in each other
+// list; no barrier), else by radix selection.  Returns the number of candidates (< k when fewer tokens are
+// allowed, src/kernels.cu:698-699); sorted[nk .. k_cap) = 0.  All NT threads; block synchronised on entry and
+// exit.
+template <int NT>
+__device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, uint64_t * sorted, SelectScratch & sc,
+                           int k, int k_cap) {
     const int tid = threadIdx.x;
     const int total = lists * len;
     int nk;
     if (lists <= 8) {
-        for (int j = tid; j < k_cap; j += kThreads) sorted[j] = 0ull;
+        for (int j = tid; j < k_cap; j += NT) sorted[j] = 0ull;
         if (tid == 0) sc.count = 0u;
         __syncthreads();
         int mine = 0;
-        for (int i = tid; i < total; i += kThreads) {
+        for (int i = tid; i < total; i += NT) {
             const uint64_t key = buf[i];
             if (key == 0ull) continue;
             ++mine;
@@ -179,12 +196,12 @@ __device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel,
         }
         if (mine) atomicAdd(&sc.count, (uint32_t) mine);
         __syncthreads();
-        nk = (int) min(sc.count, (uint32_t) k);  // fewer than k allowed tokens: src/kernels.cu:698-699
+        nk = (int) min(sc.count, (uint32_t) k);
     } else {
         if (tid == 0) sc.count = 0u;
         __syncthreads();
         // squeeze out the empty slots (the order does not matter to the selection)
-        for (int base = 0; base < total; base += kThreads) {
+        for (int base = 0; base < total; base += NT) {
             const int i = base + tid;
             const uint64_t key = i < total ? buf[i] : 0ull;
             __syncthreads();
@@ -193,14 +210,26 @@ __device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel,
         }
         const int n = (int) sc.count;
         __syncthreads();
-        const uint64_t tau = block_kth_key(buf, n, k, sc);
-        nk = block_take(buf, n, k, tau, sel, sc);  // fewer than k allowed tokens: src/kernels.cu:698-699
-        for (int j = nk + tid; j < k_cap; j += kThreads) sorted[j] = 0ull;
-        block_rank_sort(sel, nk, sorted);
+        const uint64_t tau = block_kth_key<NT>(buf, n, k, sc);
+        nk = block_take<NT>(buf, n, k, tau, sel, sc);
+        for (int j = nk + tid; j < k_cap; j += NT) sorted[j] = 0ull;
+        block_rank_sort<NT>(sel, nk, sorted);
         __syncthreads();
     }
+    return nk;
+}
+
+// The tail of k_sample (src/kernels.cu:698-720) over the nk sorted candidates: candidate softmax, top-p / min-p
+// cut, temperature weights, Philox draw.  exp and the quotients are per-element and run in parallel; the three
+// running sums keep the reference's left-to-right order: `sum` then `cum` on thread 0, the weight prefix (which
+// is both wsum and the acc of the inverse-CDF walk) on thread 32.  qj aliases the selection staging (k_cap
+// doubles).  All NT threads; block synchronised on entry.  p.counter is the counter of this row.
+template <int NT>
+__device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double * acc, double * qj, SelectScratch & sc,
+                          const fns_b200_params & p, int k_cap, int32_t * out_token, fns_b200_cand * out_cands) {
+    const int tid = threadIdx.x;
     if (out_cands)
-        for (int j = tid; j < k_cap; j += kThreads) out_cands[j] = key_to_cand(sorted[j]);
+        for (int j = tid; j < k_cap; j += NT) out_cands[j] = key_to_cand(sorted[j]);
     if (!out_token) return;
     if (nk == 0) {
         if (tid == 0) *out_token = -1;
@@ -211,24 +240,17 @@ __device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel,
         return;
     }
     const double v0 = (double) key_value(sorted[0]);
-    double my_p = 0.0;
-    if (tid < nk) {  // nk <= kThreads in the reference-compatible range; larger k loops below
-        const double d = (double) key_value(sorted[tid]) - v0;
-        my_p = exp(d);
-        pj[tid] = my_p;
-        acc[tid] = exp(d / p.temperature);
-    }
-    for (int j = tid + kThreads; j < nk; j += kThreads) {
+    for (int j = tid; j < nk; j += NT) {
         const double d = (double) key_value(sorted[j]) - v0;
         pj[j] = exp(d);
         acc[j] = exp(d / p.temperature);
     }
     __syncthreads();
-    double * qj = reinterpret_cast<double *>(sel);  // p_j / sum, in the staging area (k_cap doubles)
+    volatile double * sum_slot = reinterpret_cast<volatile double *>(&sc.hist[0]);
     if (tid == 0) {
         double sum = 0.0;
         for (int j = 0; j < nk; ++j) sum += pj[j];
-        *reinterpret_cast<volatile double *>(&sc.hist[0]) = sum;
+        *sum_slot = sum;
     } else if (tid == 32) {
         double run = 0.0;
         for (int j = 0; j < nk; ++j) {
@@ -238,8 +260,8 @@ __device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel,
     }
     __syncthreads();
     {
-        const double sum = *reinterpret_cast<volatile double *>(&sc.hist[0]);
-        for (int j = tid; j < nk; j += kThreads) qj[j] = pj[j] / sum;
+        const double sum = *sum_slot;
+        for (int j = tid; j < nk; j += NT) qj[j] = pj[j] / sum;
     }
     __syncthreads();
     if (tid == 0) {
@@ -260,7 +282,6 @@ __device__ void finalize_row(uint64_t * buf, int lists, int len, uint64_t * sel,
         for (int j = 0; j < keep; ++j)
             if (u < acc[j]) { pick = j; break; }
         *out_token = key_id(sorted[pick]);
-        sh_keep = keep;
     }
 }
 
@@ -279,15 +300,17 @@ __device__ __forceinline__ float vector_max(const float (&xv)[VEC], uint32_t bit
     return m;
 }
 
-template <typename T, int VEC>
-__global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
-    constexpr int NV = kEpochElems / VEC;            // vectors per thread per epoch
-    constexpr int FPE = NV < 4 ? NV : 4;             // flags per thread per epoch; a flag covers NV / FPE vectors
-    constexpr int VPF = NV / FPE;
-    constexpr int kEpoch = kThreads * kEpochElems;   // elements per block per epoch (slice_len is a multiple)
-    constexpr int kWarps = kThreads / 32;
+template <typename T, int VEC, int NT>
+__global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
+    constexpr int NV = kEpochElems / VEC;                    // vectors per thread per epoch
+    constexpr int FPE = (NV < 4 ? NV : 4) / (NT / 256) > 0 ? (NV < 4 ? NV : 4) / (NT / 256) : 1;  // flags per epoch
+    constexpr int VPF = NV / FPE;                            // vectors per flag (a "group")
+    constexpr int GPR = 16 / (VPF * VEC) > 0 ? 16 / (VPF * VEC) : 1;  // groups per thread per pass-2 round
+    constexpr int kEpoch = NT * kEpochElems;                 // elements per block per epoch
+    constexpr int kWarps = NT / 32;
     constexpr uint32_t kVecBits = VEC == 32 ? 0xffffffffu : (1u << VEC) - 1u;
-    constexpr int kWordsPerVec = kThreads * VEC / 32;  // bit-set words between two vectors of one thread
+    constexpr int kWordsPerVec = NT * VEC / 32;              // bit-set words between two vectors of one thread
+    static_assert(FPE * (NT == 256 ? 16 : 32) <= 64, "flag word too small for the longest slice");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = blockIdx.y, slice = blockIdx.x;
@@ -298,25 +321,33 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
     const int n_s = max(0, min(a.vocab, lo + a.slice_len) - lo);
     uint64_t * out = a.cand + ((size_t) row * a.slices + slice) * a.k_cap;
 
-    // shared memory: candidate buffer | selection staging | sorted | p, acc (fp64) | slice bit set | history table
-    // | list of the table's occupied slots
+    // shared memory: candidate buffer | selection staging | sorted | p, acc (fp64) | slice bit set |
+    // history table: offsets, counts | list of the table's occupied slots | their logits | stash: tags, values
     uint64_t * buf = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t * sel = buf + a.cap;
     uint64_t * sorted = sel + a.k_cap;
     double * pj = reinterpret_cast<double *>(sorted + a.k_cap);
     double * acc = pj + a.k_cap;
     uint32_t * eff = reinterpret_cast<uint32_t *>(acc + a.k_cap);
-    int * htab = reinterpret_cast<int *>(eff + a.slice_len / 32);
-    int * hlist = htab + a.ht_size;
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(hlist + a.ht_size / 2);
+    int * hoff = reinterpret_cast<int *>(eff + a.slice_len / 32);
+    uint32_t * hcnt = reinterpret_cast<uint32_t *>(hoff + a.ht_size);
+    int * hlist = reinterpret_cast<int *>(hcnt + a.ht_size);
+    float * hval = reinterpret_cast<float *>(hlist + a.ht_size / 2);  // raw logits of the listed ids
+    uint32_t * stash_tag = reinterpret_cast<uint32_t *>(hval + a.ht_size / 2);
+    float * stash_val = reinterpret_cast<float *>(stash_tag + a.stash_cap);  // [stash_cap][max(VEC, 4)]
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(stash_val + (size_t) a.stash_cap * (VEC < 4 ? 4 : VEC));
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
     const uint32_t id0 = (uint32_t) (a.id_base + lo);
 
     FNS_PHASE_BEGIN
-    // The first history ids are requested before anything else (their addresses do not depend on the row's
-    // history length, which is itself still in flight).
+#ifdef FNS_PHASE_TIMING
+    if (k == 12345) atomicExch(a.err, 3);  // consumes the parameters: phase 10 = their arrival
+    FNS_PHASE(10)
+#endif
+    // The first history ids are requested before anything else: their addresses do not depend on the row's
+    // history length, which is itself still in flight.
     const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
     const bool use_hist = any_pen && a.ht_size > 0 && n_s > 0;
     const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
@@ -325,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
     if (use_hist && hrow) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int j = u * kThreads + tid;
+            const int j = u * NT + tid;
             if (j < (int) a.history_stride) ids0[u] = hrow[j];
         }
     }
@@ -337,43 +368,64 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
     const int n_pen = n_hist + (a.draft ? col : 0);
 
     // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
-    // streaming loop needs no bounds handling.  A warp's 32 words lie in one epoch (128 words): the epochs that
-    // have any allowed element are collected in sh.epoch_mask, the others are never visited.
+    // streaming loop needs no bounds handling.  A warp's 32 words lie in one epoch: the epochs that have any
+    // allowed element are collected in sh.epoch_mask, the others are never visited.
     if (tid == 0) {
         sh.n_cand = 0u;
         sh.thr_key = 0ull;
         sh.epoch_mask = 0u;
         sh.n_list = 0u;
+        sh.n_stash = 0u;
     }
     if (tid < kWarps) sh.warp_bound[tid] = 0u;
     {
-        int4 * h4 = reinterpret_cast<int4 *>(htab);
-        for (int i = tid; i < a.ht_size / 4; i += kThreads) h4[i] = make_int4(kHashEmpty, kHashEmpty, kHashEmpty, kHashEmpty);
+        int4 * h4 = reinterpret_cast<int4 *>(hoff);  // offsets empty, counts (the array behind them) zero
+        for (int i = tid; i < a.ht_size / 2; i += NT) {
+            const int fill = i < a.ht_size / 4 ? kHashEmpty : 0;
+            h4[i] = make_int4(fill, fill, fill, fill);
+        }
     }
     __syncthreads();
     const int words = (n_s + 31) >> 5;
-    for (int w = tid; w < a.slice_len / 32; w += kThreads) {
-        uint32_t m = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
-        if (w == words - 1 && (n_s & 31)) m &= (1u << (n_s & 31)) - 1u;
-        eff[w] = m;
-        if (__any_sync(kFull, m != 0u) && lane == 0) atomicOr(&sh.epoch_mask, 1u << (w >> 7));
+    for (int w0 = 0; w0 < a.slice_len / 32; w0 += NT * 4) {  // slice_len / 32 is a multiple of NT / 2
+        uint32_t m[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {  // four independent loads in flight
+            const int w = w0 + u * NT + tid;
+            m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int w = w0 + u * NT + tid;
+            if (w >= a.slice_len / 32) continue;  // uniform per warp: NT / 2 divides slice_len / 32
+            if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
+            eff[w] = m[u];
+            if (__any_sync(kFull, m[u] != 0u) && lane == 0) atomicOr(&sh.epoch_mask, 1u << (w / (kEpoch / 32)));
+        }
     }
     uint64_t best = 0ull;      // k == 1: this thread's best key
     uint32_t lost = 0u;        // elements of the current round that found the buffer full
-    FNS_PHASE(0)
+    float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    bool hv_ok[4] = {false, false, false, false};
+    FNS_MARK(0)
+#ifdef FNS_PHASE_TIMING
+    if (ids0[0] == 0x7ffffff0 || n_hist == 0x7ffffff0) atomicExch(a.err, 3);  // consumes the prefetched ids
+    FNS_MARK(11)
+#endif
 
     // 2. Penalties.  The row's history (plus the draft prefix of a verification column) is scattered into a
     // shared hash table: in-slice offset -> occurrence count; the thread that claims a slot also appends it to
-    // a list, so the distinct ids can be walked densely afterwards.  Each distinct id is then removed from the
-    // bit set and offered once as a candidate with its penalised value, so the streaming passes pay nothing for
-    // penalties.  Traffic: 4 bytes per history id (every slice reads the list; it stays in L2).
+    // a list, so the distinct ids can be walked densely afterwards.  Each distinct id then leaves the bit set
+    // (whether the mask allowed it is kept in bit 30 of its list entry), so the streaming passes pay nothing for
+    // penalties; its penalised value is offered as a candidate after pass 1, when a bound exists that most of
+    // them fail.  Traffic: 4 bytes per history id (every slice reads the list; it stays in L2).
     if (use_hist && n_pen > 0) {
         const uint32_t hmask = (uint32_t) a.ht_size - 1u;
-        for (int j0 = 0; j0 < n_pen; j0 += kThreads * 4) {
+        for (int j0 = 0; j0 < n_pen; j0 += NT * 4) {
             int32_t ids[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {  // four independent loads in flight
-                const int j = j0 + u * kThreads + tid;
+                const int j = j0 + u * NT + tid;
                 if (j0 == 0 && hrow) ids[u] = j < n_hist ? ids0[u] : (j < n_pen ? drow[j - n_hist] : -1);
                 else ids[u] = j < n_hist ? hrow[j] : (j < n_pen ? drow[j - n_hist] : -1);
             }
@@ -381,83 +433,52 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
             for (int u = 0; u < 4; ++u) {
                 const uint32_t off = (uint32_t) (ids[u] - a.id_base - lo);
                 if (off >= (uint32_t) n_s || ids[u] < a.id_base) continue;
-                uint32_t h = (off * 2654435761u) & hmask;
+                // double hashing: with linear probing the clusters at load 1/2 make the slowest lane of a warp walk
+                // dozens of slots, each a dependent shared-memory access
+                uint32_t h = (off * 2654435761u) >> a.ht_shift;
+                const uint32_t step = ((off * 0x85EBCA6Bu) >> a.ht_shift) | 1u;
                 for (int probe = 0; probe <= a.ht_size; ++probe) {
                     if (probe == a.ht_size) { atomicExch(a.err, 2); break; }  // table full: cannot happen (load <= 1/2)
-                    int cur = htab[h];
-                    if (cur == kHashEmpty) {
-                        cur = atomicCAS(&htab[h], kHashEmpty, (int) ((off << 16) | 1u));
-                        if (cur == kHashEmpty) {
-                            hlist[atomicAdd(&sh.n_list, 1u)] = (int) h;
-                            break;
+                    int cur = hoff[h];
+                    if (cur == kHashEmpty) cur = atomicCAS(&hoff[h], kHashEmpty, (int) off);  // the old value
+                    if (cur == kHashEmpty || (uint32_t) cur == off) {
+                        const bool claimed = cur == kHashEmpty;
+#ifndef FNS_DBG_NOCNT
+                        atomicAdd(&hcnt[h], 1u);
+#endif
+#ifdef FNS_DBG_NOLIST
+                        if (false) {
+#else
+                        if (claimed) {
+#endif
+                            const cooperative_groups::coalesced_group cg = cooperative_groups::coalesced_threads();
+                            uint32_t base = 0u;
+                            if (cg.thread_rank() == 0) base = atomicAdd(&sh.n_list, cg.size());
+                            hlist[cg.shfl(base, 0) + cg.thread_rank()] = (int) h;
                         }
-                    }
-                    if (((uint32_t) cur >> 16) == off) {
-                        atomicAdd(&htab[h], 1);
                         break;
                     }
-                    h = (h + 1u) & hmask;
+                    h = (h + step) & hmask;
                 }
             }
         }
         __syncthreads();
+        FNS_PHASE(8)
         const int n_list = (int) sh.n_list;
-        // penalised key of a table entry; v is the raw logit.  0 if the result is not finite.
-        auto entry_key = [&](int e, float v) -> uint64_t {
-            const uint32_t off = (uint32_t) e >> 16;
-            const float cnt = (float) ((uint32_t) e & 0xffffu);
-            // each step rounded on its own: no fused multiply-add
-            v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
-            v = __fsub_rn(v, __fmul_rn(p.frequency, cnt));
-            v = __fsub_rn(v, p.presence);
-            return is_finite(v) ? make_key(v, id0 + off) : 0ull;
-        };
-        // 32 list entries per thread between two votes (one `lost` bit each), four at a time so that their
-        // logit loads overlap
-        for (int j0 = 0; j0 < n_list; j0 += kThreads * 32) {
-            for (int g = 0; g < 8 && j0 + g * 4 * kThreads < n_list; ++g) {
-                int e[4];
-                float v[4];
-                bool ok[4];
+        for (int j = tid; j < n_list; j += NT) {
+            const int h = hlist[j];
+            const uint32_t off = (uint32_t) hoff[h];
+            const uint32_t bit = 1u << (off & 31);
+            if (atomicAnd(&eff[off >> 5], ~bit) & bit) hlist[j] = h | (1 << 30);
+        }
+        FNS_MARK(9)
+        // the logits of the first ids of the list are requested now and parked in shared memory once the first
+        // epochs of pass 1 are in flight, so that nobody waits for them
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int j = j0 + (g * 4 + u) * kThreads + tid;
-                    e[u] = j < n_list ? htab[hlist[j]] : kHashEmpty;
-                    ok[u] = false;
-                    if (e[u] != kHashEmpty) {
-                        const uint32_t off = (uint32_t) e[u] >> 16;
-                        const uint32_t bit = 1u << (off & 31);
-                        ok[u] = (atomicAnd(&eff[off >> 5], ~bit) & bit) != 0u;  // allowed by the grammar mask
-                        if (ok[u]) v[u] = to_float(x[off]);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (!ok[u]) continue;
-                    const uint64_t key = entry_key(e[u], v[u]);
-                    if (key == 0ull) continue;
-                    if (k == 1) {
-                        best = key > best ? key : best;
-                    } else if (key >= *(volatile uint64_t *) &sh.thr_key && !push(key, buf, sh, a.cap)) {
-                        lost |= 1u << (g * 4 + u);
-                    }
-                }
-            }
-            if (k > 1) {
-                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                    compact(buf, sel, k, a.cap, sh);
-                    const uint64_t thr_key = sh.thr_key;
-                    uint32_t still = 0u;
-                    for (uint32_t m = lost; m; m &= m - 1u) {
-                        const int b = __ffs(m) - 1;
-                        const int e = htab[hlist[j0 + b * kThreads + tid]];
-                        const uint64_t key = entry_key(e, to_float(x[(uint32_t) e >> 16]));
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
-                    }
-                    lost = still;
-                    if (!__syncthreads_or(lost != 0u)) break;
-                }
-            }
+        for (int u = 0; u < 4; ++u) {
+            const int j = u * NT + tid;
+            hv_ok[u] = j < n_list && (hlist[j] & (1 << 30));
+            if (hv_ok[u]) hv[u] = to_float(x[hoff[hlist[j] & ~(1 << 30)]]);
         }
     }
     __syncthreads();
@@ -474,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
                     if (k == 1) {
                         best = key > best ? key : best;
                     } else if (!push(key, buf, sh, a.cap)) {
-                        atomicExch(a.err, 1);  // cannot happen: at most VEC - 1 keys after a vote that left room
+                        atomicExch(a.err, 1);  // cannot happen: the buffer is empty here
                     }
                 }
             }
@@ -485,17 +506,16 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
 
     // 3. Pass 1 over the slice: maxima only.  An epoch gives every thread NV vectors (16 elements); two epochs
     // are in flight (the loads of the next one are issued before the current one is reduced); a vector whose
-    // elements the bit set excludes is not loaded.  Nothing is appended here and no element is looked at
-    // individually: every thread keeps the maximum of what it has seen, and a 64-bit flag word marks the vector
-    // groups whose maximum reaches the running bound.  The bound needs no buffer: if r = ceil(k / warps) lanes
-    // of EVERY warp hold a maximum >= v, the slice has at least k elements >= v, so nothing below v can be among
-    // its best k.  Each warp finds its r-th largest lane maximum with r warp-wide max reductions and publishes
-    // it; the bound is the minimum over the warps (for k = 1: the maximum).  It is refreshed after epochs 1, 2,
-    // 4, 8, 16 and once more at the end.
+    // elements the bit set excludes is not loaded.  Every thread keeps the maximum of what it has seen, and a
+    // 64-bit flag word marks the vector groups whose maximum reaches the running bound.  The bound needs no
+    // buffer: if r = ceil(k / warps) lanes of EVERY warp hold a maximum >= v, the slice has at least k elements
+    // >= v, so nothing below v can be among its best k.  Each warp finds its r-th largest lane maximum with r
+    // warp-wide max reductions and publishes it; the bound is the minimum over the warps (for k = 1: the
+    // maximum).  It is refreshed after epochs 1, 2, 4, 8, 16 and once more at the end.
     const uint32_t * effp = eff + ((tid * VEC) >> 5);
     const int bshift = (tid * VEC) & 31;
     const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
-    const bool bounded = r_need <= 32;             // otherwise (k > 256) every group is flagged
+    const bool bounded = r_need <= 32;             // otherwise every group is flagged
     float tmax = -INFINITY;                        // this thread's maximum so far
     float thr_v = -FLT_MAX;                        // the bound as a float: x < thr_v cannot be a candidate
     uint32_t thr_word = 0u;
@@ -528,20 +548,15 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             mb[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-            if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * kThreads * NV + i * kThreads + tid) * VEC), xv[i]);
+            if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
         }
     };
     auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
-        float gm[FPE];
+        float vmx[NV];
 #pragma unroll
-        for (int g = 0; g < FPE; ++g) {
-            gm[g] = -INFINITY;
-#pragma unroll
-            for (int u = 0; u < VPF; ++u) {
-                const int i = g * VPF + u;
-                if (mb[i]) gm[g] = fmaxf(gm[g], vector_max<VEC>(xv[i], mb[i]));
-            }
-            tmax = fmaxf(tmax, gm[g]);
+        for (int i = 0; i < NV; ++i) {
+            vmx[i] = mb[i] ? vector_max<VEC>(xv[i], mb[i]) : -INFINITY;
+            tmax = fmaxf(tmax, vmx[i]);
         }
         if (bounded && (done & (done + 1)) == 0) {  // done = 0, 1, 3, 7, 15
             refresh();
@@ -550,7 +565,38 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
         }
         ++done;
 #pragma unroll
-        for (int g = 0; g < FPE; ++g) flags |= (uint64_t) (gm[g] >= thr_v ? 1u : 0u) << (ep * FPE + g);
+        for (int g = 0; g < FPE; ++g) {
+            uint32_t q = 0u;  // the vectors of this group that reach the bound
+#pragma unroll
+            for (int u = 0; u < VPF; ++u) q |= (vmx[g * VPF + u] >= thr_v ? 1u : 0u) << u;
+            if (!q) continue;
+            // Their values go to the stash (pass 2 then needs no memory access).  The group's slots are reserved
+            // together: if they do not all fit, none is used (the reserved ones are marked void) and the flag of
+            // the group makes pass 2 read it again, so no element can be offered twice.
+            const uint32_t want = (uint32_t) __popc(q);
+            uint32_t slot = atomicAdd(&sh.n_stash, want);
+            const bool fits = slot + want <= (uint32_t) a.stash_cap;
+            if (!fits) flags |= 1ull << (ep * FPE + g);
+#pragma unroll
+            for (int u = 0; u < VPF; ++u) {
+                if (!((q >> u) & 1u)) continue;
+                const int i = g * VPF + u;
+                if (fits) {
+                    float4 * dst = reinterpret_cast<float4 *>(stash_val + (size_t) slot * (VEC < 4 ? 4 : VEC));
+                    if constexpr (VEC == 1) {
+                        dst[0] = make_float4(xv[i][0], 0.0f, 0.0f, 0.0f);
+                    } else {
+#pragma unroll
+                        for (int w4 = 0; w4 < VEC / 4; ++w4)
+                            dst[w4] = make_float4(xv[i][4 * w4], xv[i][4 * w4 + 1], xv[i][4 * w4 + 2], xv[i][4 * w4 + 3]);
+                    }
+                    stash_tag[slot] = (uint32_t) (ep * NV + i) | ((uint32_t) tid << 9) | (mb[i] << 18);
+                } else if (slot < (uint32_t) a.stash_cap) {
+                    stash_tag[slot] = 0xffffffffu;  // void
+                }
+                ++slot;
+            }
+        }
     };
     {
         uint32_t todo = sh.epoch_mask;  // the same for every thread: read after the barrier above
@@ -564,9 +610,16 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
         uint32_t ma[NV], mb[NV];
         int ea = next(), eb = -1;
         if (ea >= 0) issue(ea, xa, ma);
+        bool parked = false;
         while (ea >= 0) {
             eb = next();
             if (eb >= 0) issue(eb, xb, mb);
+            if (!parked) {
+                parked = true;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (hv_ok[u]) hval[u * NT + tid] = hv[u];
+            }
             reduce(ea, xa, ma);
             if (eb < 0) break;
             ea = next();
@@ -574,17 +627,126 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
             reduce(eb, xb, mb);
         }
     }
+    if (done == 0) {  // no epoch had an allowed element: the parked logits were not stored yet
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (hv_ok[u]) hval[u * NT + tid] = hv[u];
+    }
     if (bounded && done > 1) {  // the final bound (after one epoch the first refresh already is)
         refresh();
         __syncthreads();
         read_bound();
+    } else {
+        __syncthreads();  // the stash is complete
     }
     FNS_PHASE(2)
 
-    // Pass 2: only the flagged groups are read again (from L1 / L2: the slice was just streamed) and their
-    // elements compared with the final bound, one group per thread and round.  What passes is appended; the block
-    // votes once per round on whether to compact (buffer filling up, or an append that found it full, which is
-    // then offered again after the compaction).
+    // The penalised candidates: every distinct history id that the mask allowed, with its penalised value,
+    // against the bound (the bound came from the other elements alone, which can only make it lower than the
+    // true k-th best: still a valid bar).  32 list entries per thread between two votes (one `lost` bit each),
+    // four at a time so that their logit loads overlap.
+    uint64_t thr_key = (uint64_t) thr_word << 32;
+    if (use_hist && n_pen > 0) {
+        const int n_list = (int) sh.n_list;
+        auto entry_key = [&](int h, float v) -> uint64_t {  // v: the raw logit; 0 if the result is not finite
+            const float cnt = (float) hcnt[h];
+            // each step rounded on its own: no fused multiply-add
+            v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
+            v = __fsub_rn(v, __fmul_rn(p.frequency, cnt));
+            v = __fsub_rn(v, p.presence);
+            return is_finite(v) ? make_key(v, id0 + (uint32_t) hoff[h]) : 0ull;
+        };
+        for (int j0 = 0; j0 < n_list; j0 += NT * 32) {
+            for (int g = 0; g < 8 && j0 + g * 4 * NT < n_list; ++g) {
+                int h[4];
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + (g * 4 + u) * NT + tid;
+                    const int e = j < n_list ? hlist[j] : 0;
+                    h[u] = (e & (1 << 30)) ? (e & ~(1 << 30)) : -1;
+                    if (h[u] >= 0) v[u] = j < 4 * NT ? hval[j] : to_float(x[hoff[h[u]]]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (h[u] < 0) continue;
+                    const uint64_t key = entry_key(h[u], v[u]);
+                    if (key == 0ull) continue;
+                    if (k == 1) best = key > best ? key : best;
+                    else if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (g * 4 + u);
+                }
+            }
+            if (k > 1 && n_list + VEC > a.trigger) {  // uniform: only a long list can fill the buffer
+                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                    compact<NT>(buf, sel, k, a.cap, sh);
+                    const uint64_t tk = sh.thr_key;
+                    if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+                    uint32_t still = 0u;
+                    for (uint32_t m = lost; m; m &= m - 1u) {
+                        const int b = __ffs(m) - 1;
+                        const int h = hlist[j0 + b * NT + tid] & ~(1 << 30);
+                        const uint64_t key = entry_key(h, to_float(x[hoff[h]]));
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+                    }
+                    lost = still;
+                    if (!__syncthreads_or(lost != 0u)) break;
+                }
+            }
+        }
+    }
+
+    // Pass 2, first the stash: the vectors that reached the bound when they were streamed, values and all, are
+    // compared with the final bound; what passes is appended.  No memory access, no rounds: the entries are
+    // spread evenly over the threads.
+    {
+        constexpr int SE = VEC < 4 ? 4 : VEC;  // floats per stash entry
+        const int n_st = (int) min(sh.n_stash, (uint32_t) a.stash_cap);
+        // a vote is needed only if the appends could fill the buffer.  The decision must be the same in every
+        // thread, so it uses counts that no longer change here (the append cursor itself is moving): what the
+        // penalty list and the ragged end can have appended at most, plus every stashed element
+        const bool may_fill = (int) sh.n_list + VEC + n_st * VEC > a.trigger;
+        for (int i0 = 0; i0 < n_st; i0 += NT) {
+            const int i = i0 + tid;
+            uint32_t ebase = 0u;
+            const uint32_t tag = i < n_st ? stash_tag[i] : 0xffffffffu;
+            if (tag != 0xffffffffu) {
+                const int vi = (int) (tag & 511u), owner = (int) ((tag >> 9) & 511u);
+                const uint32_t bits = tag >> 18;
+                const int ep = vi / NV, iv = vi - ep * NV;
+                ebase = (uint32_t) ((ep * NT * NV + iv * NT + owner) * VEC);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    const float xi = stash_val[(size_t) i * SE + j];
+                    if (((bits >> j) & 1u) && xi >= thr_v && xi <= FLT_MAX) {
+                        const uint64_t key = make_key(xi, id0 + ebase + (uint32_t) j);
+                        if (k == 1) best = key > best ? key : best;
+                        else if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << j;
+                    }
+                }
+            }
+            if (k > 1 && may_fill) {
+                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                    compact<NT>(buf, sel, k, a.cap, sh);
+                    const uint64_t tk = sh.thr_key;
+                    if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+                    uint32_t still = 0u;
+                    for (uint32_t m = lost; m; m &= m - 1u) {
+                        const int b = __ffs(m) - 1;
+                        const uint64_t key = make_key(stash_val[(size_t) i * SE + b], id0 + ebase + (uint32_t) b);
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+                    }
+                    lost = still;
+                    if (!__syncthreads_or(lost != 0u)) break;
+                }
+            }
+        }
+    }
+
+    // Pass 2, then the groups that did not fit the stash (none unless the input is adversarial or k is large):
+    // they are read again (from L1 / L2: the slice was just streamed) and their
+    // elements compared with the final bound, up to GPR groups per thread and round, their loads issued
+    // together.  What passes is appended; the block votes once per round on whether to compact (buffer filling
+    // up, or an append that found it full, which is then offered again after the compaction).
     if (k == 1) {
         while (flags) {
             const int b = __ffsll((long long) flags) - 1;
@@ -593,7 +755,7 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
 #pragma unroll
             for (int u = 0; u < VPF; ++u) {
                 const int i = g * VPF + u;
-                const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC;
+                const int e = (ep * NT * NV + i * NT + tid) * VEC;
                 const uint32_t bits = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
                 if (!bits) continue;
                 float xv[VEC];
@@ -608,47 +770,58 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
             }
         }
     } else {
-        uint64_t thr_key = (uint64_t) thr_word << 32;
-        {
-            const uint64_t tk = sh.thr_key;  // a compaction of the penalty phase may have left a higher bar
-            if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
-        }
         while (__syncthreads_or(flags != 0ull)) {
-            int ep = 0, g = 0;
-            const bool has = flags != 0ull;
-            if (has) {
-                const int b = __ffsll((long long) flags) - 1;
-                flags &= flags - 1ull;
-                ep = b / FPE;
-                g = b - ep * FPE;
+            int eoff[GPR * VPF];      // element offset of each vector of this round (-1: none)
+            uint32_t bits[GPR * VPF];
+            float xv[GPR * VPF][VEC];
+#pragma unroll
+            for (int q = 0; q < GPR; ++q) {
+                int b = -1;
+                if (flags) {
+                    b = __ffsll((long long) flags) - 1;
+                    flags &= flags - 1ull;
+                }
+                const int ep = b / FPE, g = b - ep * FPE;
 #pragma unroll
                 for (int u = 0; u < VPF; ++u) {
                     const int i = g * VPF + u;
-                    const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC;
-                    const uint32_t bits = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-                    if (!bits) continue;
-                    float xv[VEC];
-                    load_vec<T, VEC>(x + e, xv);
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        if (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) {
-                            const uint64_t key = make_key(xv[j], id0 + (uint32_t) (e + j));
-                            if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (u * VEC + j);
+                    const int v = q * VPF + u;
+                    eoff[v] = -1;
+                    bits[v] = 0u;
+                    if (b >= 0) {
+                        bits[v] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+                        if (bits[v]) {
+                            eoff[v] = (ep * NT * NV + i * NT + tid) * VEC;
+                            load_vec<T, VEC>(x + eoff[v], xv[v]);
                         }
                     }
                 }
             }
+#pragma unroll
+            for (int v = 0; v < GPR * VPF; ++v) {
+                if (eoff[v] < 0) continue;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    if (((bits[v] >> j) & 1u) && xv[v][j] >= thr_v && xv[v][j] <= FLT_MAX) {
+                        const uint64_t key = make_key(xv[v][j], id0 + (uint32_t) (eoff[v] + j));
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (v * VEC + j);
+                    }
+                }
+            }
             while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                compact(buf, sel, k, a.cap, sh);
+                compact<NT>(buf, sel, k, a.cap, sh);
                 const uint64_t tk = sh.thr_key;
                 if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
                 uint32_t still = 0u;
-                for (uint32_t m = lost; m; m &= m - 1u) {
-                    const int b = __ffs(m) - 1;
-                    const int i = g * VPF + b / VEC;
-                    const int e = (ep * kThreads * NV + i * kThreads + tid) * VEC + (b % VEC);
-                    const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
-                    if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+#pragma unroll
+                for (int v = 0; v < GPR * VPF; ++v) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        if (!((lost >> (v * VEC + j)) & 1u)) continue;
+                        const int e = eoff[v] + j;
+                        const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << (v * VEC + j);
+                    }
                 }
                 lost = still;
                 if (!__syncthreads_or(lost != 0u)) break;
@@ -658,7 +831,12 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
     __syncthreads();
     FNS_PHASE(3)
 
-    // 4. The slice's answer: its best k keys in the total order.
+    // 4. The slice's answer: its best k keys in the total order.  A row that is one slice goes straight on to
+    // the draw; otherwise the list goes to global memory and the last block of the row merges.
+    const bool whole_row = a.slices == 1;
+    p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
+    int32_t * tok = a.out_tokens ? a.out_tokens + row : nullptr;
+    fns_b200_cand * oc = a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr;
     if (k == 1) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -670,17 +848,39 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
         if (tid == 0) {
             uint64_t b = sh.red[0];
             for (int w = 1; w < kWarps; ++w) b = sh.red[w] > b ? sh.red[w] : b;
-            out[0] = b;
+            if (whole_row) {
+                if (tok) *tok = b ? key_id(b) : -1;
+                if (oc) oc[0] = key_to_cand(b);
+            } else {
+                out[0] = b;
+            }
+        }
+        if (whole_row) {
+            if (oc)
+                for (int j = 1 + tid; j < a.k_cap; j += NT) oc[j] = key_to_cand(0ull);
+            return;
         }
     } else {
         const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
-        const uint64_t tau = block_kth_key(buf, n, k, sh.sc);
-        const int got = block_take(buf, n, k, tau, sel, sh.sc);
-        block_rank_sort(sel, got, out);
-        for (int j = got + tid; j < k; j += kThreads) out[j] = 0ull;
+        uint64_t * dst = whole_row ? sorted : out;
+        int got;
+        if (n <= kRankSelectMax) {
+            got = block_rank_select<NT>(buf, n, k, dst);
+        } else {
+            const uint64_t tau = block_kth_key<NT>(buf, n, k, sh.sc);
+            got = block_take<NT>(buf, n, k, tau, sel, sh.sc);
+            block_rank_sort<NT>(sel, got, dst);
+        }
+        for (int j = got + tid; j < (whole_row ? a.k_cap : k); j += NT) dst[j] = 0ull;
+        if (whole_row) {
+            __syncthreads();
+            FNS_PHASE(4)
+            draw_tail<NT>(sorted, got, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
+            FNS_PHASE(5)
+            return;
+        }
     }
     FNS_PHASE(4)
-    if (!a.tickets) return;
 
     // 5. The last block of the row to get here merges the slices' lists and draws.  Nobody waits: every block
     // takes a ticket after its list is visible, and the one that draws the last ticket does the work.
@@ -690,16 +890,14 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
         const unsigned t = atomicAdd(&a.tickets[row], 1u);
         sh.is_last = t == (unsigned) a.slices - 1u;
         if (sh.is_last) a.tickets[row] = 0u;  // ready for the next launch
-        sh.n_keys = 0u;
     }
     __syncthreads();
     if (!sh.is_last) return;
     __threadfence();
     const uint64_t * lists = a.cand + (size_t) row * a.slices * a.k_cap;
-    p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
     if (k == 1) {  // greedy: the largest of the slices' best keys, no sort, no draw
         uint64_t b = 0ull;
-        for (int l = tid; l < a.slices; l += kThreads) {
+        for (int l = tid; l < a.slices; l += NT) {
             const uint64_t key = __ldcg(lists + (size_t) l * a.k_cap);
             b = key > b ? key : b;
         }
@@ -712,57 +910,50 @@ __global__ void __launch_bounds__(kThreads, 4) k_select(const SelectArgs a) {
         __syncthreads();
         if (tid == 0) {
             for (int w = 1; w < kWarps; ++w) b = sh.red[w] > b ? sh.red[w] : b;
-            if (a.out_tokens) a.out_tokens[row] = b ? key_id(b) : -1;
-            if (a.out_cands) a.out_cands[(size_t) row * a.k_cap] = key_to_cand(b);
+            if (tok) *tok = b ? key_id(b) : -1;
+            if (oc) oc[0] = key_to_cand(b);
         }
-        if (a.out_cands)
-            for (int j = 1 + tid; j < a.k_cap; j += kThreads) a.out_cands[(size_t) row * a.k_cap + j] = key_to_cand(0ull);
+        if (oc)
+            for (int j = 1 + tid; j < a.k_cap; j += NT) oc[j] = key_to_cand(0ull);
         FNS_PHASE(5)
         return;
     }
     // the slices' lists, each sorted, side by side in the buffer: [slices][k]
-    for (int i = tid; i < a.slices * k; i += kThreads) {
+    for (int i = tid; i < a.slices * k; i += NT) {
         const int l = i / k, j = i - l * k;
         buf[i] = __ldcg(lists + (size_t) l * a.k_cap + j);
     }
     __syncthreads();
-    finalize_row(buf, a.slices, k, sel, sorted, pj, acc, sh.sc, sh.keep, p, k, a.k_cap,
-                 a.out_tokens ? a.out_tokens + row : nullptr,
-                 a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
+    const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, sh.sc, k, a.k_cap);
+    draw_tail<NT>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
     FNS_PHASE(5)
 }
 
 // ---- finalize as a kernel of its own -------------------------------------------------------------------------
+constexpr int kFinalThreads = 256;
+
 struct FinalArgs {
-    const uint64_t * keys;        // internal lists (sorted keys, 0 = empty), or
-    const fns_b200_cand * cands;  // external lists; entry j of list l of row r at r * row_stride + l * list_stride + j
+    const fns_b200_cand * cands;  // entry j of list l of row r at r * row_stride + l * list_stride + j
     int lists;
-    int list_len;  // entries to read from each list
+    int list_len;
     int64_t list_stride;
     int64_t row_stride;
     int k_cap;
-    int n_draft;
     const fns_b200_params * params;
-    fns_b200_params p0;
     int32_t * out_tokens;      // may be null (merge only)
     fns_b200_cand * out_cands; // may be null; [rows][k_cap]
 };
 
 struct FinalShared {
     SelectScratch sc;
-    uint32_t n_keys;
-    int keep;
 };
 
-__global__ void __launch_bounds__(kThreads) k_finalize(const FinalArgs a) {
+__global__ void __launch_bounds__(kFinalThreads) k_finalize(const FinalArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x;
     const int row = blockIdx.x;
-    const int W = a.n_draft + 1, win = row / W, col = row - win * W;
-    fns_b200_params p = a.params ? a.params[win] : a.p0;
-    p.counter += (uint64_t) col;
+    const fns_b200_params p = a.params[row];
     const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
-    const int take_len = a.keys ? min(a.list_len, k) : a.list_len;  // internal lists hold exactly the row's k
 
     // shared memory: all keys of the row | selection staging | sorted result | p / acc (fp64)
     uint64_t * buf = reinterpret_cast<uint64_t *>(smem_raw);
@@ -772,17 +963,17 @@ __global__ void __launch_bounds__(kThreads) k_finalize(const FinalArgs a) {
     double * acc = pj + a.k_cap;
     FinalShared & sh = *reinterpret_cast<FinalShared *>(acc + a.k_cap);
 
-    // the row's lists side by side: [lists][take_len]
+    // the row's lists side by side: [lists][list_len]
     const size_t row_base = (size_t) row * a.row_stride;
-    for (int i = tid; i < a.lists * take_len; i += kThreads) {
-        const int l = i / take_len, j = i - l * take_len;
-        const size_t at = row_base + (size_t) l * a.list_stride + j;
-        buf[i] = a.keys ? a.keys[at] : cand_to_key(a.cands[at]);
+    for (int i = tid; i < a.lists * a.list_len; i += kFinalThreads) {
+        const int l = i / a.list_len, j = i - l * a.list_len;
+        buf[i] = cand_to_key(a.cands[row_base + (size_t) l * a.list_stride + j]);
     }
     __syncthreads();
-    finalize_row(buf, a.lists, take_len, sel, sorted, pj, acc, sh.sc, sh.keep, p, k, a.k_cap,
-                 a.out_tokens ? a.out_tokens + row : nullptr,
-                 a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
+    const int nk = merge_lists<kFinalThreads>(buf, a.lists, a.list_len, sel, sorted, sh.sc, k, a.k_cap);
+    draw_tail<kFinalThreads>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap,
+                             a.out_tokens ? a.out_tokens + row : nullptr,
+                             a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
 }
 
 // a = number of leading columns whose token equals the draft (tools/fns_serve/fns_serve.cpp:492-508).
@@ -828,6 +1019,7 @@ struct fns_b200_sampler {
     int max_rows, max_vocab, k_cap, max_history;
     int sm_count;
     int force_slices;
+    int force_threads;
     uint64_t * cand;   // [rows][slices][k_cap] sorted keys of the slices
     size_t cand_entries;
     unsigned * tickets;  // [max_rows], zero between launches
@@ -842,8 +1034,7 @@ struct fns_b200_sampler {
 namespace {
 
 struct Plan {
-    int slices, slice_len, cap, trigger, ht_size, vec;
-    bool fused;  // the last block of a row merges and draws inside k_select
+    int threads, slices, slice_len, cap, trigger, ht_size, vec, stash_cap;
     size_t smem_select;
 };
 
@@ -863,40 +1054,49 @@ int fail_cuda(fns_b200_sampler * s, cudaError_t e, const char * where) {
     return FNS_B200_ERR_CUDA;
 }
 
-// Launch geometry.  Slices per row: about twelve 256-thread blocks per SM over the whole call, so that the
-// hardware block scheduler evens out rows whose masks make them cheap or expensive; no slice shorter than 2048
-// elements; the slices' lists of one row must fit the merge (kMaxMergeKeys) and, for the fused finalize, the
-// candidate buffer of the block that does it.
+// Launch geometry.  With at least one row per SM a row is one slice and a block has 512 threads: two blocks fit
+// an SM, so up to 2 * SMs rows stream at once, and setup, history and draw are paid once per row.  With fewer
+// rows a row is cut into slices of 256-thread blocks, about four per SM in total, so that the whole GPU works on
+// the call.  A slice is a whole number of epochs (16 elements per thread) and at most 16 (256 threads) or 32
+// (512 threads) of them; the slices' lists of one row must fit the merge (kMaxMergeKeys).
 bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
     const int k_cap = s->k_cap;
-    const int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
+    pl.threads = s->force_threads > 0 ? s->force_threads : (s->force_slices > 0 ? 256 : (rows >= s->sm_count ? 512 : 256));
+    const int epoch = pl.threads * kEpochElems;
+    const int max_slice_len = (pl.threads == 256 ? 16 : 32) * epoch;
+    const int min_slices = (vocab + max_slice_len - 1) / max_slice_len;
     int max_slices = kMaxMergeKeys / k_cap;
     if (max_slices > kMaxSlices) max_slices = kMaxSlices;
     if (min_slices > max_slices) return false;
-    int want = s->force_slices > 0 ? s->force_slices : (s->sm_count * 12 + rows - 1) / rows;
-    const int by_len = (vocab + kSliceAlign - 1) / kSliceAlign;  // no slice shorter than one epoch
-    if (s->force_slices <= 0 && want > by_len) want = by_len;
+    int want;
+    if (s->force_slices > 0) want = s->force_slices;
+    else if (pl.threads == 512) want = 1;
+    else want = (s->sm_count * 4 + rows - 1) / rows;
+    const int by_len = (vocab + epoch - 1) / epoch;  // no slice shorter than one epoch
+    if (want > by_len) want = by_len;
     if (s->force_slices <= 0 && want > 64) want = 64;
     if (want < min_slices) want = min_slices;
     if (want > max_slices) want = max_slices;
     if (want < 1) want = 1;
-    pl.slice_len = round_up((vocab + want - 1) / want, kSliceAlign);
-    if (pl.slice_len > kMaxSliceLen) pl.slice_len = kMaxSliceLen;
+    pl.slice_len = round_up((vocab + want - 1) / want, epoch);
+    if (pl.slice_len > max_slice_len) pl.slice_len = max_slice_len;
     pl.slices = (vocab + pl.slice_len - 1) / pl.slice_len;
     pl.vec = aligned ? (dtype == FNS_B200_BF16 ? 8 : 4) : 1;
     const int base_cap = 4 * k_cap > 2048 ? 4 * k_cap : 2048;
     pl.trigger = base_cap / 2;
     pl.cap = base_cap;
-    pl.fused = true;
     if (pl.slices * k_cap > pl.cap) pl.cap = pl.slices * k_cap;  // room to merge the row's lists
     pl.ht_size = 0;
     if (hist_bound > 0) {
         const int distinct = hist_bound < pl.slice_len ? hist_bound : pl.slice_len;
         pl.ht_size = next_pow2(2 * distinct);
-        if (pl.ht_size < kThreads) pl.ht_size = kThreads;
+        if (pl.ht_size < 1024) pl.ht_size = 1024;
     }
-    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.ht_size * 6 +
-                     sizeof(SelectShared) + 16;
+    // stash: 16 KB of flagged vectors (tag + max(vec, 4) floats each)
+    const int entry_floats = pl.vec < 4 ? 4 : pl.vec;
+    pl.stash_cap = 16384 / (4 * entry_floats + 4) / 4 * 4;  // a multiple of 4: what follows stays 16-byte aligned
+    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.ht_size * 12 +
+                     (size_t) pl.stash_cap * (4 * entry_floats + 4) + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
 
@@ -904,9 +1104,9 @@ size_t final_smem(int lists, int list_len, int k_cap) {
     return (size_t) lists * list_len * 8 + (size_t) k_cap * 8 * 4 + sizeof(FinalShared) + 16;
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int NT>
 cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
-    auto kern = k_select<T, VEC>;
+    auto kern = k_select<T, VEC, NT>;
     static bool configured[64] = {};  // per device: the opt-in to large dynamic shared memory is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -915,15 +1115,21 @@ cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStr
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<dim3((unsigned) a.slices, (unsigned) rows), kThreads, smem, st>>>(a);
+    kern<<<dim3((unsigned) a.slices, (unsigned) rows), NT, smem, st>>>(a);
     return cudaGetLastError();
 }
 
-cudaError_t launch_select(const SelectArgs & a, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
+template <int NT>
+cudaError_t launch_select_nt(const SelectArgs & a, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
     if (dtype == FNS_B200_BF16)
-        return vec == 8 ? launch_select_t<__nv_bfloat16, 8>(a, rows, smem, st)
-                        : launch_select_t<__nv_bfloat16, 1>(a, rows, smem, st);
-    return vec == 4 ? launch_select_t<float, 4>(a, rows, smem, st) : launch_select_t<float, 1>(a, rows, smem, st);
+        return vec == 8 ? launch_select_t<__nv_bfloat16, 8, NT>(a, rows, smem, st)
+                        : launch_select_t<__nv_bfloat16, 1, NT>(a, rows, smem, st);
+    return vec == 4 ? launch_select_t<float, 4, NT>(a, rows, smem, st) : launch_select_t<float, 1, NT>(a, rows, smem, st);
+}
+
+cudaError_t launch_select(const SelectArgs & a, int threads, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
+    return threads == 512 ? launch_select_nt<512>(a, dtype, vec, rows, smem, st)
+                          : launch_select_nt<256>(a, dtype, vec, rows, smem, st);
 }
 
 cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
@@ -936,7 +1142,7 @@ cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    k_finalize<<<(unsigned) rows, kThreads, smem, st>>>(a);
+    k_finalize<<<(unsigned) rows, kFinalThreads, smem, st>>>(a);
     return cudaGetLastError();
 }
 
@@ -996,45 +1202,21 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.cap = pl.cap;
     a.trigger = pl.trigger;
     a.ht_size = pl.ht_size;
+    a.ht_shift = 32;
+    for (int t = pl.ht_size; t > 1; t >>= 1) --a.ht_shift;
+    a.stash_cap = pl.stash_cap;
     a.cand = s->cand;
-    a.tickets = pl.fused ? s->tickets : nullptr;
+    a.tickets = s->tickets;
     a.out_tokens = out_tokens;
     a.out_cands = out_cands;
     a.err = s->err;
     const bool prof = s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size();
     if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3], st);
-    const cudaError_t e = launch_select(a, dtype, pl.vec, rows, pl.smem_select, st);
+    const cudaError_t e = launch_select(a, pl.threads, dtype, pl.vec, rows, pl.smem_select, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "select launch");
     ++s->launches;
-    if (prof) {
+    if (prof) {  // the merge and the draw happen inside k_select: the record closes here
         cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 1], st);
-        if (pl.fused) {  // no finalize launch follows: close the record here
-            cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 2], st);
-            ++s->prof_calls;
-        }
-    }
-    return FNS_B200_OK;
-}
-
-int run_final_internal(fns_b200_sampler * s, const Plan & pl, int rows, int n_draft, const fns_b200_params * params,
-                       const fns_b200_params * p0, int32_t * out_tokens, fns_b200_cand * out_cands, cudaStream_t st) {
-    if (pl.fused) return FNS_B200_OK;  // k_select already merged and drew
-    FinalArgs f{};
-    f.keys = s->cand;
-    f.lists = pl.slices;
-    f.list_len = s->k_cap;
-    f.list_stride = s->k_cap;
-    f.row_stride = (int64_t) pl.slices * s->k_cap;
-    f.k_cap = s->k_cap;
-    f.n_draft = n_draft;
-    f.params = params;
-    if (p0) f.p0 = *p0;
-    f.out_tokens = out_tokens;
-    f.out_cands = out_cands;
-    const cudaError_t e = launch_final(f, rows, st);
-    if (e != cudaSuccess) return fail_cuda(s, e, "finalize launch");
-    ++s->launches;
-    if (s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size()) {
         cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3 + 2], st);
         ++s->prof_calls;
     }
@@ -1061,6 +1243,7 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
     s->k_cap = k_cap;
     s->max_history = max_history;
     s->force_slices = 0;
+    s->force_threads = 0;
     s->launches = 0;
     s->prof_on = false;
     s->prof_calls = 0;
@@ -1158,6 +1341,12 @@ int fns_b200_set_slices(fns_b200_sampler * s, int slices) {
     return FNS_B200_OK;
 }
 
+int fns_b200_set_threads(fns_b200_sampler * s, int threads) {
+    if (!s || (threads != 0 && threads != 256 && threads != 512)) return FNS_B200_ERR_ARG;
+    s->force_threads = threads;
+    return FNS_B200_OK;
+}
+
 int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int history_bound, int * slices,
                   int * slice_len, int * smem_bytes) {
     if (!s || vocab <= 0 || rows <= 0) return FNS_B200_ERR_ARG;
@@ -1179,8 +1368,7 @@ int fns_b200_sample_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     Plan pl;
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
                         history_len, nullptr, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
-    if (rc != FNS_B200_OK) return rc;
-    return run_final_internal(s, pl, rows, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream);
+    return rc;
 }
 
 int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
@@ -1193,8 +1381,7 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
     Plan pl;
     int rc = run_select(s, logits, dtype, vocab, vocab, 1, 0, mask, (vocab + 31) / 32, nullptr, 0, nullptr, nullptr, 0,
                         nullptr, params_host, out_token, nullptr, (cudaStream_t) stream, pl);
-    if (rc != FNS_B200_OK) return rc;
-    return run_final_internal(s, pl, 1, 0, nullptr, params_host, out_token, nullptr, (cudaStream_t) stream);
+    return rc;
 }
 
 int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
@@ -1208,8 +1395,7 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, id_base, masks, mask_stride_words, history,
                         history_stride, history_len, nullptr, 0, params, nullptr, nullptr, out_cands,
                         (cudaStream_t) stream, pl);
-    if (rc != FNS_B200_OK) return rc;
-    return run_final_internal(s, pl, rows, 0, params, nullptr, nullptr, out_cands, (cudaStream_t) stream);
+    return rc;
 }
 
 int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len,
@@ -1228,7 +1414,6 @@ int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, in
     f.list_stride = list_stride;
     f.row_stride = row_stride;
     f.k_cap = s->k_cap;
-    f.n_draft = 0;
     f.params = params;
     f.out_tokens = out_tokens;
     f.out_cands = out_cands;
@@ -1251,8 +1436,6 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
     int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
                         history_len, draft, n_draft, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
-    rc = run_final_internal(s, pl, rows, n_draft, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream);
-    if (rc != FNS_B200_OK) return rc;
     k_accept<<<(unsigned) ((windows + 127) / 128), 128, 0, (cudaStream_t) stream>>>(out_tokens, draft, n_draft, windows,
                                                                                   out_accept);
     const cudaError_t e = cudaGetLastError();
@@ -1265,8 +1448,8 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
 // development aid (not part of the ABI header): reads and clears the phase clocks
 int fns_b200_debug_phases(unsigned long long * out8) {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 8);
-    unsigned long long zero[8] = {};
+    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 16);
+    unsigned long long zero[16] = {};
     cudaMemcpyToSymbol(fnsb::g_phase, zero, sizeof zero);
     return 0;
 }

@@ -58,6 +58,7 @@ SYMBOLS = [
     "fns_b200_io_advance",
     "fns_b200_plan",
     "fns_b200_set_slices",
+    "fns_b200_set_threads",
     "fns_b200_launch_count",
     "fns_b200_profile_begin",
     "fns_b200_profile_end",
@@ -123,6 +124,7 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_io_advance.argtypes = [vp, i32, vp]
     lib.fns_b200_plan.argtypes = [vp, i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.fns_b200_set_slices.argtypes = [vp, i32]
+    lib.fns_b200_set_threads.argtypes = [vp, i32]
     f64p = ctypes.POINTER(ctypes.c_double)
     lib.fns_b200_launch_count.argtypes = [vp]
     lib.fns_b200_profile_begin.argtypes = [vp, i32]
@@ -209,6 +211,9 @@ class Sampler:
 
     def set_slices(self, slices: int):
         self._check(self.lib.fns_b200_set_slices(self.handle, slices))
+
+    def set_threads(self, threads: int):
+        self._check(self.lib.fns_b200_set_threads(self.handle, threads))
 
     def plan(self, dtype: int, vocab: int, rows: int, history_bound: int = 0):
         s, l, b = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()

@@ -215,6 +215,9 @@ int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, in
 /* Overrides the number of slices per row (0 = automatic).  For tests that must show that results do not depend
  * on the launch geometry. */
 int fns_b200_set_slices(fns_b200_sampler * s, int slices);
+/* Overrides the block size of the select kernel: 256 (sliced rows), 512 (one block per row when it fits), 0 =
+ * automatic.  For the same tests. */
+int fns_b200_set_threads(fns_b200_sampler * s, int threads);
 
 #ifdef __cplusplus
 }
