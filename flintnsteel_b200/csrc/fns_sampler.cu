@@ -82,6 +82,7 @@ struct SelectArgs {
     int ht_size;     // history table slots (power of two >= 1024), 0: no table
     int ht_shift;    // 32 - log2(ht_size): the table index is the high bits of a multiplicative hash
     int stash_cap;   // entries of the flagged-vector stash
+    int list_cap;    // entries of the allowed-vector list (it shares the stash's memory)
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
     int32_t * out_tokens;       // [rows], may be null
@@ -95,7 +96,9 @@ struct SelectShared {
     uint32_t n_cand;      // append cursor; may run past cap (the excess was not stored: see `lost`)
     uint32_t epoch_mask;  // epochs of the slice that have an allowed element
     uint32_t n_list;      // occupied slots of the history table
-    uint32_t n_stash;     // flagged groups kept in shared memory for pass 2
+    uint32_t n_stash;     // flagged vectors kept in shared memory for pass 2
+    uint32_t n_av;        // vectors of the slice with an allowed element
+    uint32_t n_vl;        // cursor of the allowed-vector list
     int keep;
     int is_last;
     __align__(16) uint32_t warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
@@ -376,6 +379,8 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         sh.epoch_mask = 0u;
         sh.n_list = 0u;
         sh.n_stash = 0u;
+        sh.n_av = 0u;
+        sh.n_vl = 0u;
     }
     if (tid < kWarps) sh.warp_bound[tid] = 0u;
     {
@@ -598,6 +603,100 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             }
         }
     };
+    // How many vectors of the slice have an allowed element?  (One bit per vector: the OR of its mask bits.)
+    auto vector_units = [](uint32_t m) -> uint32_t {
+        if constexpr (VEC == 1) return m;
+        if constexpr (VEC == 4) return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x11111111u;
+        m |= m >> 4;
+        return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
+    };
+    {
+        uint32_t cnt = 0u;
+        for (int w = tid; w < a.slice_len / 32; w += NT) cnt += (uint32_t) __popc(vector_units(eff[w]));
+        cnt = __reduce_add_sync(kFull, cnt);
+        if (lane == 0 && cnt) atomicAdd(&sh.n_av, cnt);
+    }
+    __syncthreads();
+    constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
+    const int n_av = (int) sh.n_av;
+    const bool sparse = n_av <= min(NT * LPT, a.list_cap);
+    if (sparse) {
+        // 3a. Few allowed vectors (a grammar mask that admits little): no epochs.  The allowed vectors are listed
+        // from the bit set, every thread requests all of its (at most LPT) at once, and after ONE memory round
+        // trip the bound is known and the candidates are appended straight from registers.
+        uint32_t * vlist = stash_tag;  // the stash is not used on this path
+        for (int w = tid; w < a.slice_len / 32; w += NT) {
+            uint32_t t = vector_units(eff[w]);
+            if (!t) continue;
+            uint32_t at = atomicAdd(&sh.n_vl, (uint32_t) __popc(t));
+            for (; t; t &= t - 1u) vlist[at++] = (uint32_t) (w * (32 / VEC) + (__ffs(t) - 1) / VEC);
+        }
+        __syncthreads();
+        float xv[LPT][VEC];
+        uint32_t mb[LPT];
+        int ev[LPT];
+#pragma unroll
+        for (int u = 0; u < LPT; ++u) {
+            const int j = u * NT + tid;
+            mb[u] = 0u;
+            ev[u] = 0;
+            if (j < n_av) {
+                ev[u] = (int) vlist[j] * VEC;
+                mb[u] = (eff[ev[u] >> 5] >> (ev[u] & 31)) & kVecBits;
+                load_vec<T, VEC>(x + ev[u], xv[u]);
+            }
+        }
+        {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (hv_ok[u]) hval[u * NT + tid] = hv[u];
+        }
+        float vmx[LPT];
+#pragma unroll
+        for (int u = 0; u < LPT; ++u) {
+            vmx[u] = mb[u] ? vector_max<VEC>(xv[u], mb[u]) : -INFINITY;
+            tmax = fmaxf(tmax, vmx[u]);
+        }
+        if (bounded) {
+            refresh();
+            __syncthreads();
+            read_bound();
+        }
+        done = 1;
+        const uint64_t tk0 = (uint64_t) thr_word << 32;
+#pragma unroll
+        for (int u = 0; u < LPT; ++u) {
+            if (!(vmx[u] >= thr_v)) continue;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                if (((mb[u] >> j) & 1u) && xv[u][j] >= thr_v && xv[u][j] <= FLT_MAX) {
+                    const uint64_t key = make_key(xv[u][j], id0 + (uint32_t) (ev[u] + j));
+                    if (k == 1) best = key > best ? key : best;
+                    else if (key >= tk0 && !push(key, buf, sh, a.cap)) lost |= 1u << (u * VEC + j);
+                }
+            }
+        }
+        if (k > 1 && n_av * VEC + VEC > a.trigger) {  // uniform: only then can the buffer fill
+            uint64_t tk = tk0;
+            while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                compact<NT>(buf, sel, k, a.cap, sh);
+                if (sh.thr_key > tk) tk = sh.thr_key;
+                uint32_t still = 0u;
+#pragma unroll
+                for (int u = 0; u < LPT; ++u) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        if (!((lost >> (u * VEC + j)) & 1u)) continue;
+                        const uint64_t key = make_key(xv[u][j], id0 + (uint32_t) (ev[u] + j));
+                        if (key >= tk && !push(key, buf, sh, a.cap)) still |= 1u << (u * VEC + j);
+                    }
+                }
+                lost = still;
+                if (!__syncthreads_or(lost != 0u)) break;
+            }
+        }
+        __syncthreads();
+    } else
     {
         uint32_t todo = sh.epoch_mask;  // the same for every thread: read after the barrier above
         auto next = [&]() -> int {
@@ -1205,6 +1304,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.ht_shift = 32;
     for (int t = pl.ht_size; t > 1; t >>= 1) --a.ht_shift;
     a.stash_cap = pl.stash_cap;
+    a.list_cap = pl.stash_cap * ((pl.vec < 4 ? 4 : pl.vec) + 1);  // 32-bit words in the stash's memory
     a.cand = s->cand;
     a.tickets = s->tickets;
     a.out_tokens = out_tokens;

@@ -51,17 +51,19 @@ class RowSharded:
         return self.backend.sample_rows(logits, params, out, masks=masks, history=history, history_len=history_len)
 
     def gather_tokens(self, local_tokens, total_rows: int):
-        """Optional: every rank receives all tokens (rows must split evenly for the single-call form)."""
+        """Optional: every rank receives all tokens, in row order.  Shards of unequal size are padded to the
+        largest for the collective (equal contributions on every backend) and trimmed afterwards."""
         if self.world == 1:
             return local_tokens
-        if total_rows % self.world == 0:
-            out = torch.empty(total_rows, dtype=local_tokens.dtype, device=local_tokens.device)
-            dist.all_gather_into_tensor(out, local_tokens.contiguous(), group=self.group)
+        sizes = [hi - lo for lo, hi in (shard_range(total_rows, r, self.world) for r in range(self.world))]
+        width = max(sizes)
+        padded = torch.full((width,), -1, dtype=local_tokens.dtype, device=local_tokens.device)
+        padded[: local_tokens.numel()] = local_tokens
+        out = torch.empty(self.world * width, dtype=local_tokens.dtype, device=local_tokens.device)
+        dist.all_gather_into_tensor(out, padded, group=self.group)
+        if all(n == width for n in sizes):
             return out
-        sizes = [shard_range(total_rows, r, self.world) for r in range(self.world)]
-        parts = [torch.empty(hi - lo, dtype=local_tokens.dtype, device=local_tokens.device) for lo, hi in sizes]
-        dist.all_gather(parts, local_tokens.contiguous(), group=self.group)
-        return torch.cat(parts)
+        return torch.cat([out[r * width: r * width + n] for r, n in enumerate(sizes)])
 
 
 class VocabSharded:
@@ -88,7 +90,8 @@ class VocabSharded:
         self.backend.select_rows(logits_shard, params, local, id_base=self.lo, masks=masks_shard, history=history,
                                  history_len=history_len, vocab=self.hi - self.lo)
         if self.world > 1:
-            dist.all_gather_into_tensor(gathered, local, group=self.group)
+            # the output is the ranks' [rows][k_cap] blocks one after the other (dim 0 concatenation)
+            dist.all_gather_into_tensor(gathered.view(self.world * rows, self.k_cap, 2), local, group=self.group)
         else:
             gathered = local[None]
         # gathered is [world][rows][k_cap]: list l of row r starts at l * rows * k_cap + r * k_cap
