@@ -32,6 +32,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <mutex>
 #include <vector>
 
 namespace fnsb {
@@ -1588,3 +1589,72 @@ int fns_b200_io_advance(int32_t * io, int pos, void * stream) {
 }
 
 }  // extern "C"
+
+// ---- sampling without any allocation ----------------------------------------------------------------------
+// For hosts that may not allocate GPU memory when they sample: engines that hand the whole device to their own
+// arena at start-up and leave nothing for cudaMalloc, and call sites where an allocation, which synchronises
+// the device, is not allowed.  The candidate lists, the per-row tickets and the error flag that a handle would
+// own live in one file-scope device array instead.  Every GPU that loads the library carries this array until
+// the process exits.
+namespace {
+
+constexpr int kNoAllocRows = 64;                       // rows per call
+constexpr int kNoAllocK = 64;                          // k_cap, the reference's kSampleMaxK
+constexpr size_t kNoAllocCand = (size_t) kNoAllocRows * 64 * kNoAllocK;  // keys: 64 rows x 64 slices x 64 = 2 MiB
+constexpr size_t kNoAllocBytes = kNoAllocCand * sizeof(uint64_t) + kNoAllocRows * sizeof(unsigned) + 256;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+std::mutex g_noalloc_lock;
+unsigned char * g_noalloc_ptr[64];  // per device: the array's DEVICE address (its name in host code is not one)
+
+}  // namespace
+
+extern "C" int fns_b200_sample_rows_noalloc(int device, const void * logits, int dtype, int64_t row_stride, int vocab,
+                                            int rows, const uint32_t * masks, int64_t mask_stride_words,
+                                            const int32_t * history, int64_t history_stride,
+                                            const int32_t * history_len, const fns_b200_params * params,
+                                            int32_t * out_tokens, void * stream, char * error_text, int error_len) {
+    auto fail_text = [&](int code, const char * what) {
+        if (error_text && error_len > 0) std::snprintf(error_text, (size_t) error_len, "%s", what);
+        return code;
+    };
+    if (device < 0 || device >= 64) return fail_text(FNS_B200_ERR_ARG, "device outside [0, 64)");
+    if (!out_tokens || !params) return fail_text(FNS_B200_ERR_ARG, "out_tokens or params null");
+    if (rows > kNoAllocRows) return fail_text(FNS_B200_ERR_CAPACITY, "rows > 64: the static scratch holds 64 rows per call");
+    DeviceGuard g(device);
+    if (!g.ok) return fail_text(FNS_B200_ERR_CUDA, "cannot make the device current");
+    unsigned char * base = nullptr;
+    {
+        // Set-up, once per device, with that device current: ask the runtime where the array lives on it.
+        std::lock_guard<std::mutex> hold(g_noalloc_lock);
+        if (!g_noalloc_ptr[device]) {
+            void * p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) return fail_text(FNS_B200_ERR_CUDA, cudaGetErrorString(e));
+            g_noalloc_ptr[device] = static_cast<unsigned char *>(p);
+        }
+        base = g_noalloc_ptr[device];
+    }
+    fns_b200_sampler s{};  // a handle on the stack whose workspace is the static array; nothing is allocated
+    s.device = device;
+    s.max_rows = kNoAllocRows;
+    s.max_vocab = 0x7fffffff;
+    s.k_cap = kNoAllocK;
+    s.max_history = FNS_B200_MAX_HISTORY;
+    if (cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return fail_text(FNS_B200_ERR_CUDA, "cudaDeviceGetAttribute failed");
+    s.cand = reinterpret_cast<uint64_t *>(base);
+    s.cand_entries = kNoAllocCand;
+    s.tickets = reinterpret_cast<unsigned *>(base + kNoAllocCand * sizeof(uint64_t));
+    s.err = reinterpret_cast<int *>(base + kNoAllocCand * sizeof(uint64_t) + kNoAllocRows * sizeof(unsigned));
+    // The array keeps whatever the last call left: the tickets and the error flag must start at zero.
+    const cudaError_t e = cudaMemsetAsync(s.tickets, 0, kNoAllocRows * sizeof(unsigned) + sizeof(int), (cudaStream_t) stream);
+    if (e != cudaSuccess) return fail_text(FNS_B200_ERR_CUDA, cudaGetErrorString(e));
+    Plan pl;
+    const int rc = run_select(&s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history,
+                              history_stride, history_len, nullptr, 0, params, nullptr, out_tokens, nullptr,
+                              (cudaStream_t) stream, pl);
+    if (rc != FNS_B200_OK) return fail_text(rc, s.msg);
+    return FNS_B200_OK;
+}

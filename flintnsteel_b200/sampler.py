@@ -48,6 +48,7 @@ SYMBOLS = [
     "fns_b200_k_cap",
     "fns_b200_sample_rows",
     "fns_b200_sample_one",
+    "fns_b200_sample_rows_noalloc",
     "fns_b200_select_rows",
     "fns_b200_finalize_rows",
     "fns_b200_verify_accept",
@@ -114,6 +115,8 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_k_cap.argtypes = [vp]
     lib.fns_b200_sample_rows.argtypes = [vp, vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
     lib.fns_b200_sample_one.argtypes = [vp, vp, i32, i32, vp, vp, i32, vp, vp, vp]
+    lib.fns_b200_sample_rows_noalloc.argtypes = [i32, vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp,
+                                                 ctypes.c_char_p, i32]
     lib.fns_b200_select_rows.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, i64, vp, i64, vp, vp, vp, vp]
     lib.fns_b200_finalize_rows.argtypes = [vp, vp, i32, i32, i64, i64, i32, vp, vp, vp, vp]
     lib.fns_b200_verify_accept.argtypes = [vp, vp, i32, i64, i32, i32, i32, vp, vp, i64, vp, i64, vp, vp, vp, vp, vp]

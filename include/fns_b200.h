@@ -107,6 +107,29 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
                         const int32_t * history, int history_len, const fns_b200_params * params_host,
                         int32_t * out_token, void * stream);
 
+/* Sampling for hosts that must not allocate GPU memory: the same result as fns_b200_sample_rows with k_cap = 64,
+ * without a handle.  (No counterpart in the reference; its sampler keeps its candidates in file-scope device
+ * arrays too, src/kernels.cu:601-602, but nothing there is exposed as an interface.)
+ *
+ * Who needs it: an engine that gives the whole GPU to its own memory arena at start-up, so that a later cudaMalloc
+ * fails or is forbidden, and call sites where an allocation is unacceptable because it synchronises the device.
+ * fns_b200_create allocates; this entry point, and everything it calls, never calls cudaMalloc, cudaFree or any
+ * allocating routine.  What a handle would own (the slices' candidate lists, one ticket per row, an error flag)
+ * lives in a static device array of 2 MiB + 512 bytes that every GPU loading the library holds until exit.
+ *
+ * Limits: rows <= 64 per call, k_cap fixed at 64 (params.top_k <= 0 or > 64 means 64); larger calls are refused
+ * with FNS_B200_ERR_CAPACITY and a text in error_text (may be NULL).  All other arguments as
+ * fns_b200_sample_rows; `device` is the GPU that owns the buffers.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device): make
+ * that first call before starting any stream capture.
+ * All calls on a GPU share the one array, which keeps the previous call's contents (this call clears what has to
+ * start at zero): calls that overlap on the GPU, on any streams, race with each other; issue them on one stream
+ * or order them with events. */
+int fns_b200_sample_rows_noalloc(int device, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
+                                 const uint32_t * masks, int64_t mask_stride_words, const int32_t * history,
+                                 int64_t history_stride, const int32_t * history_len, const fns_b200_params * params,
+                                 int32_t * out_tokens, void * stream, char * error_text, int error_len);
+
 /* First half of the path only: per-row top-k candidates of a vocabulary SHARD, in the total order.
  * The reference does the same per slice in k_topk_part (src/kernels.cu:624-648); here a shard is the slice
  * that one GPU owns.  `id_base` is the global id of the shard's element 0: history ids are global, reported
