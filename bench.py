@@ -32,6 +32,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "sampler rows/s (V=151936 fp32, mask+penalties+top-k/p, 256 sessions per GPU)"
 WORKLOAD = "sessions256"
+# dram__bytes_read.sum + dram__bytes_write.sum per k_select launch, from the ncu captures summarised under profiles/
+NCU_TRAFFIC_BYTES = 25.4e6
+NCU_TRAFFIC_BYTES_DENSE = 188.9e6
 
 
 def measured_peaks():
@@ -116,7 +119,7 @@ def run_b200(args):
     # ---- inputs: `batches` distinct 256-row batches per rank, resident in HBM --------------------------------
     host = [wl.session_batch(seed=1000 * rank + b, rows=rows) for b in range(args.batches)]
     vocab = host[0].vocab
-    row_bytes = host[0].row_bytes()
+    row_bytes = host[0].row_bytes() - (4 * host[0].masks.shape[1] if args.no_masks else 0)
     dev_in = []
     for w in host:
         dev_in.append(dict(
@@ -126,9 +129,9 @@ def run_b200(args):
     out = torch.empty(rows, dtype=torch.int32, device=dev)
     sampler = Sampler(local, max_rows=rows, max_vocab=vocab, k_cap=64, max_history=host[0].history.shape[1])
 
-    def step(i):
+    def step(i, masked=not args.no_masks):
         d = dev_in[i % len(dev_in)]
-        sampler.sample_rows(d["logits"], d["params"], out, masks=d["masks"], history=d["history"],
+        sampler.sample_rows(d["logits"], d["params"], out, masks=d["masks"] if masked else None, history=d["history"],
                             history_len=d["history_len"])
 
     def barrier():
@@ -179,6 +182,15 @@ def run_b200(args):
     peak, peak_kind = measured_peaks()
     sel_avg_s = sel_ms / max(calls, 1) / 1e3
     achieved = rows * row_bytes / sel_avg_s / 1e9 if sel_avg_s > 0 else 0.0
+    # the same rows with every id allowed: no vector can be skipped, so every logit byte comes from HBM
+    for i in range(3):
+        step(i, masked=False)
+    sampler.profile_begin(K)
+    for i in range(K):
+        step(i, masked=False)
+    dense_ms, _, dense_calls = sampler.profile_end()
+    dense_s = dense_ms / max(dense_calls, 1) / 1e3
+    dense_bytes = rows * (host[0].row_bytes() - 4 * host[0].masks.shape[1])
 
     # ---- end to end through the engine glue: host buffers in, tokens out to the host, every step -----------
     eng = Engine(local, max_rows=rows, vocab=vocab, k_cap=64, max_history=host[0].history.shape[1])
@@ -213,7 +225,7 @@ def run_b200(args):
         "metric": METRIC, "value": world * rows * K / (total_ms / 1e3), "unit": "rows/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "vocab": vocab, "k_cap": 64,
+        "config": {"workload": WORKLOAD + ("_all_ids_allowed" if args.no_masks else ""), "rows_per_gpu": rows, "vocab": vocab, "k_cap": 64,
                    "history_ids": int(host[0].history.shape[1]), "batches_rotated": len(dev_in),
                    "l2": f"{len(dev_in)} distinct batches of {rows * row_bytes / 1e6:.0f} MB rotate; each exceeds the 126 MB L2",
                    "parallelism": f"rows{world}"},
@@ -222,7 +234,15 @@ def run_b200(args):
         "roofline": {"bound": "hbm", "kernel": "k_select", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBps_nominal": achieved / 8000.0,
                      "bytes_per_launch": rows * row_bytes, "avg_launch_us": sel_avg_s * 1e6,
-                     "finalize_avg_launch_us": fin_ms / max(calls, 1) * 1e3, "traffic": args.traffic},
+                     "finalize_avg_launch_us": fin_ms / max(calls, 1) * 1e3,
+                     "traffic": args.traffic if args.traffic is not None else
+                     (NCU_TRAFFIC_BYTES if rows == 256 and not args.no_masks else None),
+                     "traffic_note": "ncu dram bytes per launch of the capture summarised under profiles/; below the "
+                                     "algorithmic bytes because vectors with no allowed id are never loaded",
+                     "all_ids_allowed": {"avg_launch_us": dense_s * 1e6, "bytes_per_launch": dense_bytes,
+                                         "achieved": dense_bytes / dense_s / 1e9 if dense_s > 0 else 0.0,
+                                         "frac": dense_bytes / dense_s / 1e9 / peak if dense_s > 0 else 0.0,
+                                         "traffic": NCU_TRAFFIC_BYTES_DENSE if rows == 256 else None}},
         "e2e": {"value": e2e_host, "unit": "rows/s", "h2d_bytes_per_step": int(rows * vocab * 4 + side_bytes),
                 "d2h_bytes_per_step": rows * 4, "steps": e2e_steps,
                 "note": "engine pick (pick_async + pick_wait): logits, masks, histories and parameters all copied "
@@ -439,6 +459,7 @@ def main():
     ap.add_argument("--batches", type=int, default=4)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--skip-extras", action="store_true", help="only the headline numbers (for profiler runs)")
+    ap.add_argument("--no-masks", action="store_true", help="every id allowed: the HBM-bound variant of the workload")
     ap.add_argument("--traffic", type=float, default=None,
                     help="dram bytes per select launch from an ncu capture (see profiles/), echoed into the line")
     args = ap.parse_args()
