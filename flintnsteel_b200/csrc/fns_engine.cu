@@ -122,6 +122,23 @@ cudaError_t stage(T * pinned, T * dev, const T * src, size_t count, cudaStream_t
     return cudaMemcpyAsync(dev, pinned, count * sizeof(T), cudaMemcpyHostToDevice, st);
 }
 
+// The device-side address of a page-locked host buffer, or NULL when the buffer is pageable (unknown to the driver).
+const void * device_view(const void * host) {
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+}
+
+// Host -> device on st: straight from the caller's buffer when it is page-locked and promised stable, else staged.
+template <typename T>
+cudaError_t bring(T * pinned, T * dev, const T * src, size_t count, bool stable, cudaStream_t st) {
+    if (stable && device_view(src)) return cudaMemcpyAsync(dev, src, count * sizeof(T), cudaMemcpyHostToDevice, st);
+    return stage(pinned, dev, src, count, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -202,7 +219,11 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
     cudaError_t err = cudaSuccess;
     const size_t esz = dtype == FNS_B200_BF16 ? 2 : 4;
     const void * lg = logits;
-    if (logits_on_host) {
+    const bool stable = (logits_on_host & FNS_B200_HOST_STABLE) != 0;
+    const void * in_place = (logits_on_host & FNS_B200_HOST_LOGITS) && stable && masks_host ? device_view(logits) : nullptr;
+    if (in_place) {
+        lg = in_place;  // the kernel loads the allowed vectors over PCIe; nothing else of the logits moves
+    } else if (logits_on_host & FNS_B200_HOST_LOGITS) {
         const size_t bytes = ((size_t) (rows - 1) * row_stride + e->vocab) * esz;
         if (bytes > e->logits_bytes) {
             cudaFree(e->logits_d);
@@ -215,14 +236,14 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
             return ecuda(e, err, "logits copy");
         lg = e->logits_d;
     }
-    if (masks_host && (err = stage(s.masks_h, s.masks_d, masks_host, (size_t) rows * e->words, st)) != cudaSuccess)
+    if (masks_host && (err = bring(s.masks_h, s.masks_d, masks_host, (size_t) rows * e->words, stable, st)) != cudaSuccess)
         return ecuda(e, err, "mask copy");
     const int32_t * hist_d = nullptr, *hist_len_d = nullptr;
     int64_t hstride = 0;
     if (history_host) {
         // rows are packed to history_stride in the staging buffer
-        if ((err = stage(s.history_h, s.history_d, history_host, (size_t) rows * history_stride, st)) != cudaSuccess ||
-            (err = stage(s.history_len_h, s.history_len_d, history_len_host, (size_t) rows, st)) != cudaSuccess)
+        if ((err = bring(s.history_h, s.history_d, history_host, (size_t) rows * history_stride, stable, st)) != cudaSuccess ||
+            (err = bring(s.history_len_h, s.history_len_d, history_len_host, (size_t) rows, stable, st)) != cudaSuccess)
             return ecuda(e, err, "history copy");
         hist_d = s.history_d;
         hist_len_d = s.history_len_d;
@@ -232,7 +253,7 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
         hist_len_d = e->sess_history_len;
         hstride = e->max_history;
     }
-    if ((err = stage(s.params_h, s.params_d, params_host, (size_t) rows, st)) != cudaSuccess)
+    if ((err = bring(s.params_h, s.params_d, params_host, (size_t) rows, stable, st)) != cudaSuccess)
         return ecuda(e, err, "params copy");
     const int rc = fns_b200_sample_rows(e->sampler, lg, dtype, row_stride, e->vocab, rows, masks_host ? s.masks_d : nullptr,
                                         e->words, hist_d, hstride, hist_len_d, s.params_d, s.tokens_d, st);

@@ -344,11 +344,14 @@ class Engine:
         return int(self.lib.fns_b200_launch_count(self.lib.fns_b200_engine_sampler(self.handle)))
 
     def pick_async(self, logits, params_host, masks_host=None, history_host=None, history_len_host=None,
-                   logits_on_host=False):
+                   logits_on_host=False, host_stable=False):
+        """``host_stable``: the host buffers stay unchanged until ``pick_wait``; page-locked ones are then read by
+        the GPU in place (FNS_B200_HOST_STABLE), and with a mask only the allowed logits cross PCIe."""
         rows = logits.shape[0]
         hs = 0 if history_host is None else history_host.shape[1]
         self._check(self.lib.fns_b200_engine_pick_async(
-            self.handle, ctypes.c_void_p(logits.data_ptr()), int(logits_on_host), _dtype_code(logits),
+            self.handle, ctypes.c_void_p(logits.data_ptr()), (1 if logits_on_host else 0) | (2 if host_stable else 0),
+            _dtype_code(logits),
             logits.stride(0), rows, _host(masks_host), _host(history_host), hs, _host(history_len_host),
             _host(params_host), _stream()))
 

@@ -200,9 +200,19 @@ const char * fns_b200_engine_last_error(const fns_b200_engine * e);
 fns_b200_sampler * fns_b200_engine_sampler(fns_b200_engine * e);
 
 /* Engine::pick_async (src/engine.cu:823-847).  logits: device [rows][row_stride], or host memory when
- * logits_on_host != 0 (then they are copied to the device inside the call).  masks_host: NULL or
+ * logits_on_host has FNS_B200_HOST_LOGITS set (then they reach the device inside the call).  masks_host: NULL or
  * [rows][ceil(vocab / 32)].  history_host: NULL to use the sessions' device-side histories (see
- * fns_b200_engine_reset / append), else [rows][history_stride] with history_len_host[rows]. */
+ * fns_b200_engine_reset / append), else [rows][history_stride] with history_len_host[rows].
+ *
+ * By default every host buffer is copied into the engine's own pinned memory before the call returns, so the
+ * caller may reuse it at once (what src/engine.cu:833 does).  With FNS_B200_HOST_STABLE the caller promises to
+ * leave its host buffers unchanged until the matching pick_wait; buffers that are page-locked (cudaHostAlloc,
+ * cudaHostRegister) are then read by the GPU where they lie: masks, histories and parameters by one DMA each
+ * without the intermediate memcpy, and - when a mask is given - the logits by the kernel itself, which loads
+ * only the 16-byte vectors that hold an allowed id, so masked-out logits never cross PCIe.  Pageable buffers are
+ * staged as before. */
+#define FNS_B200_HOST_LOGITS 1
+#define FNS_B200_HOST_STABLE 2
 int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int logits_on_host, int dtype,
                                int64_t row_stride, int rows, const uint32_t * masks_host,
                                const int32_t * history_host, int64_t history_stride,

@@ -1,0 +1,114 @@
+"""The engine glue (fns_b200_engine_*) on a GPU against the CPU oracle.
+
+The glue replaces the sampler part of the reference's Engine (src/engine.cu:715-866): pick_async / pick_wait with
+host-side masks and parameters, device-side session histories (reset / append = reset_presence / presence_mark),
+and verify for a speculative window.  Every way the inputs can reach the device must give the same tokens:
+staged pageable buffers, page-locked buffers read in place, logits on the device or on the host.
+"""
+import numpy as np
+import pytest
+
+from flintnsteel_b200 import workloads as wl
+from flintnsteel_b200.sampler import Engine, make_params
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def expected(oracle, w, k_cap=64):
+    tok, _ = oracle.sample_rows(w.logits, w.params, k_cap, w.masks, w.history, w.history_len)
+    return tok
+
+
+def test_pick_gives_the_oracle_tokens_however_the_inputs_arrive(dev, oracle):
+    w = wl.session_batch(seed=21, rows=24, vocab=40_000, history=256)
+    w.params["temperature"][::3] = 0.0  # a third of the rows greedy: no boundary cases there
+    want = expected(oracle, w)
+    eng = Engine(0, max_rows=24, vocab=w.vocab, k_cap=64, max_history=256)
+    lg_dev = torch.from_numpy(w.logits).to(dev)
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    lg_pin, masks_pin = pin(w.logits), pin(w.masks.view(np.int32))
+    hist_pin, hl_pin, par_pin = pin(w.history), pin(w.history_len), pin(w.params.view(np.uint8))
+    got = {
+        "device logits, pageable side buffers": eng.pick(
+            lg_dev, w.params, masks_host=w.masks, history_host=w.history, history_len_host=w.history_len),
+        "pageable host logits (staged)": eng.pick(
+            torch.from_numpy(w.logits), w.params, masks_host=w.masks, history_host=w.history,
+            history_len_host=w.history_len, logits_on_host=True),
+        "pinned host logits, copied": eng.pick(
+            lg_pin, par_pin, masks_host=masks_pin, history_host=hist_pin, history_len_host=hl_pin, logits_on_host=True),
+        "pinned host logits read in place": eng.pick(
+            lg_pin, par_pin, masks_host=masks_pin, history_host=hist_pin, history_len_host=hl_pin, logits_on_host=True,
+            host_stable=True),
+        "device logits, pinned side buffers read in place": eng.pick(
+            lg_dev, par_pin, masks_host=masks_pin, history_host=hist_pin, history_len_host=hl_pin, host_stable=True),
+        "stable promised but buffers pageable": eng.pick(
+            torch.from_numpy(w.logits), w.params, masks_host=w.masks, history_host=w.history,
+            history_len_host=w.history_len, logits_on_host=True, host_stable=True),
+    }
+    eng.close()
+    first = got["device logits, pageable side buffers"]
+    greedy = w.params["temperature"] <= 0
+    assert np.array_equal(first[greedy], want[greedy])
+    assert (first != want).sum() <= 1  # a draw on a CDF boundary may differ from the CPU's libm
+    for name, tokens in got.items():
+        assert np.array_equal(tokens, first), name
+
+
+def test_two_picks_in_flight_come_back_in_order(dev, oracle):
+    a = wl.session_batch(seed=31, rows=5, vocab=8192, history=16)
+    b = wl.session_batch(seed=32, rows=5, vocab=8192, history=16)
+    for w in (a, b):
+        w.params["temperature"][:] = 0.0
+    eng = Engine(0, max_rows=5, vocab=8192, k_cap=64, max_history=16)
+    la, lb = torch.from_numpy(a.logits).to(dev), torch.from_numpy(b.logits).to(dev)
+    eng.pick_async(la, a.params, masks_host=a.masks, history_host=a.history, history_len_host=a.history_len)
+    eng.pick_async(lb, b.params, masks_host=b.masks, history_host=b.history, history_len_host=b.history_len)
+    with pytest.raises(Exception):
+        eng.pick_async(la, a.params)  # a third one is refused, nothing is queued
+    ta, tb = eng.pick_wait(5), eng.pick_wait(5)
+    eng.close()
+    assert np.array_equal(ta, expected(oracle, a)) and np.array_equal(tb, expected(oracle, b))
+
+
+def test_session_histories_on_the_device_follow_the_presence_rule(dev, oracle):
+    """Greedy decoding of 3 sessions for 12 steps with a presence penalty: the engine remembers every chosen token
+    (reset_presence / presence_mark of the reference, src/engine.cu:715-731), the oracle gets the list."""
+    rows, vocab, steps = 3, 5000, 12
+    g = wl.rng(77)
+    logits = (g.standard_normal((rows, vocab)) * 0.5).astype(np.float32)
+    params = make_params(rows, temperature=0.0, top_k=1, top_p=1.0, presence=0.9, seed=1)
+    eng = Engine(0, max_rows=rows, vocab=vocab, k_cap=64, max_history=steps)
+    eng.reset()
+    lg = torch.from_numpy(logits).to(dev)
+    hist = np.zeros((rows, steps), np.int32)
+    hl = np.zeros(rows, np.int32)
+    for t in range(steps):
+        got = eng.pick(lg, params)
+        eng.append(eng.device_tokens_ptr(), 1, rows)
+        want, _ = oracle.sample_rows(logits, params, 64, None, hist, hl)
+        assert np.array_equal(got, want), f"step {t}"
+        hist[np.arange(rows), hl] = want
+        hl += 1
+    assert len(set(hist[0].tolist())) == steps  # the penalty is large enough that no token repeats
+    eng.reset()
+    again = eng.pick(lg, params)
+    eng.close()
+    assert np.array_equal(again, hist[:, 0])
+
+
+def test_verify_window_matches_the_oracle(dev, oracle):
+    sw = wl.spec_windows(seed=4, windows=16, vocab=32_000)
+    n_draft = sw.draft.shape[1]
+    eng = Engine(0, max_rows=16 * (n_draft + 1), vocab=sw.vocab, k_cap=64, max_history=0)
+    tokens, accept = eng.verify(torch.from_numpy(sw.logits).to(dev), sw.draft, sw.params)
+    eng.close()
+    for i in range(16):
+        et, ea = oracle.verify_window(sw.logits[i * (n_draft + 1):(i + 1) * (n_draft + 1)], sw.draft[i], sw.params[i:i + 1])
+        assert accept[i] == ea and np.array_equal(tokens[i], et), f"window {i}"
