@@ -53,7 +53,6 @@ __device__ unsigned long long g_phase[16];
 #define FNS_MARK(i)
 #endif
 
-constexpr int kHashEmpty = -1;
 constexpr int kMaxMergeKeys = 8192;   // k_finalize holds the lists of one row in shared memory
 constexpr int kMaxSlices = 128;
 constexpr int kEpochElems = 16;       // elements per thread and epoch
@@ -80,10 +79,8 @@ struct SelectArgs {
     int slice_len;   // a multiple of the block's epoch
     int cap;         // candidate buffer entries (>= 4 * k_cap)
     int trigger;     // compact when the buffer holds this many
-    int ht_size;     // history table slots (power of two >= 1024), 0: no table
-    int ht_shift;    // 32 - log2(ht_size): the table index is the high bits of a multiplicative hash
-    int stash_cap;   // entries of the flagged-vector stash
-    int list_cap;    // entries of the allowed-vector list (it shares the stash's memory)
+    int own_cap;     // entries of the list of owned history ids (a multiple of 4), 0: no penalties
+    int list_cap;    // entries of the allowed-vector list of a sparse slice
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
     int32_t * out_tokens;       // [rows], may be null
@@ -95,14 +92,14 @@ struct SelectShared {
     SelectScratch sc;
     uint64_t thr_key;     // the exact k-th best key of the buffer at its last compaction
     uint32_t n_cand;      // append cursor; may run past cap (the excess was not stored: see `lost`)
-    uint32_t epoch_mask;  // epochs of the slice that have an allowed element
-    uint32_t n_list;      // occupied slots of the history table
-    uint32_t n_stash;     // flagged vectors kept in shared memory for pass 2
-    uint32_t n_av;        // vectors of the slice with an allowed element
+    uint32_t n_own;       // history ids of the slice that the mask allows, each once
     uint32_t n_vl;        // cursor of the allowed-vector list
     int keep;
     int is_last;
-    __align__(16) uint32_t warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
+    __align__(16) float warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
+    uint32_t warp_top[kMaxWarps];               // per warp: its largest thread maximum (as an order word)
+    uint32_t red_cnt[kMaxWarps];                // per warp: vectors with an allowed element
+    uint32_t red_ep[kMaxWarps];                 // per warp: epochs with an allowed element
     uint64_t red[kMaxWarps];
 };
 
@@ -304,129 +301,188 @@ __device__ __forceinline__ float vector_max(const float (&xv)[VEC], uint32_t bit
     return m;
 }
 
+// The running bound of pass 1 (every thread of the block calls it at the same point).  A warp splits into
+// groups of `lanes_per_group` lanes, takes each group's largest thread maximum and publishes the smallest of
+// them: as many different lanes as there are groups have reached it.  The bound is the minimum over the warps
+// (greedy: the maximum).  Only the first call waits for every warp's share; later calls read what is there, which
+// is valid because a warp's value never decreases.
+template <int NT>
+__device__ __forceinline__ float block_bound(float tmax, float thr_v, int lanes_per_group, bool wait, bool greedy,
+                                          SelectShared & sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float v = tmax;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float other = __shfl_xor_sync(kFull, v, o);
+        v = o < lanes_per_group ? fmaxf(v, other) : fminf(v, other);
+    }
+    if (lane == 0) *(volatile float *) &sh.warp_bound[warp] = v;
+    if (wait) __syncthreads();
+    const volatile float * wb = sh.warp_bound;
+    float b = wb[0];
+#pragma unroll
+    for (int w = 1; w < NT / 32; ++w) b = greedy ? fmaxf(b, wb[w]) : fminf(b, wb[w]);
+    return fmaxf(thr_v, b);  // -inf (a warp that has seen nothing yet) leaves the bound alone
+}
+
+// 4-byte asynchronous copy global -> shared (no register is held while the load is in flight).
+__device__ __forceinline__ void copy_word_async(uint32_t * dst_shared, const void * src_global) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t) __cvta_generic_to_shared(dst_shared)),
+                 "l"(src_global)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_word_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+// The 32-bit word that holds element p[0], and the element's value out of that word.
+__device__ __forceinline__ const void * word_of(const float * p) { return p; }
+__device__ __forceinline__ const void * word_of(const __nv_bfloat16 * p) {
+    return reinterpret_cast<const void *>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t) 3);
+}
+__device__ __forceinline__ float value_in_word(uint32_t w, const float *) { return __uint_as_float(w); }
+__device__ __forceinline__ float value_in_word(uint32_t w, const __nv_bfloat16 * p) {
+    return __uint_as_float((reinterpret_cast<uintptr_t>(p) & 2) ? (w & 0xffff0000u) : (w << 16));
+}
+
+#ifdef FNS_LB1
+#define FNS_MINBLOCKS(NT) 1
+#else
+#define FNS_MINBLOCKS(NT) (1024 / NT)
+#endif
 template <typename T, int VEC, int NT>
-__global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
+__global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectArgs a) {
     constexpr int NV = kEpochElems / VEC;                    // vectors per thread per epoch
-    constexpr int FPE = (NV < 4 ? NV : 4) / (NT / 256) > 0 ? (NV < 4 ? NV : 4) / (NT / 256) : 1;  // flags per epoch
-    constexpr int VPF = NV / FPE;                            // vectors per flag (a "group")
-    constexpr int GPR = 16 / (VPF * VEC) > 0 ? 16 / (VPF * VEC) : 1;  // groups per thread per pass-2 round
+    constexpr int FPE = NV < 4 ? NV : 4;                     // flag bits per thread and epoch
+    constexpr int VPF = NV / FPE;                            // vectors per flag bit (a "group")
+    constexpr int TS = 2 * NT;                               // slots of the occurrence-count table
+    constexpr int kTShift = NT == 512 ? 22 : 23;             // 32 - log2(TS)
+    constexpr uint32_t kNoKey = 0xffffffffu;
     constexpr int kEpoch = NT * kEpochElems;                 // elements per block per epoch
     constexpr int kWarps = NT / 32;
     constexpr uint32_t kVecBits = VEC == 32 ? 0xffffffffu : (1u << VEC) - 1u;
     constexpr int kWordsPerVec = NT * VEC / 32;              // bit-set words between two vectors of one thread
-    static_assert(FPE * (NT == 256 ? 16 : 32) <= 64, "flag word too small for the longest slice");
+    constexpr int MW = 16;                                   // mask words per thread requested together
+    static_assert(32 * FPE <= 128, "two 64-bit flag words hold the longest slice");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = blockIdx.y, slice = blockIdx.x;
     const int W = a.n_draft + 1, win = row / W, col = row - win * W;
-    fns_b200_params p = a.params ? a.params[win] : a.p0;
-    const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
     const int lo = slice * a.slice_len;
     const int n_s = max(0, min(a.vocab, lo + a.slice_len) - lo);
     uint64_t * out = a.cand + ((size_t) row * a.slices + slice) * a.k_cap;
 
     // shared memory: candidate buffer | selection staging | sorted | p, acc (fp64) | slice bit set |
-    // history table: offsets, counts | list of the table's occupied slots | their logits | stash: tags, values
+    // owned history ids: offsets, logit words | mask-to-addend table
     uint64_t * buf = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t * sel = buf + a.cap;
     uint64_t * sorted = sel + a.k_cap;
     double * pj = reinterpret_cast<double *>(sorted + a.k_cap);
     double * acc = pj + a.k_cap;
     uint32_t * eff = reinterpret_cast<uint32_t *>(acc + a.k_cap);
-    int * hoff = reinterpret_cast<int *>(eff + a.slice_len / 32);
-    uint32_t * hcnt = reinterpret_cast<uint32_t *>(hoff + a.ht_size);
-    int * hlist = reinterpret_cast<int *>(hcnt + a.ht_size);
-    float * hval = reinterpret_cast<float *>(hlist + a.ht_size / 2);  // raw logits of the listed ids
-    uint32_t * stash_tag = reinterpret_cast<uint32_t *>(hval + a.ht_size / 2);
-    float * stash_val = reinterpret_cast<float *>(stash_tag + a.stash_cap);  // [stash_cap][max(VEC, 4)]
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(stash_val + (size_t) a.stash_cap * (VEC < 4 ? 4 : VEC));
+    uint32_t * own = eff + a.slice_len / 32;
+    uint32_t * oval = own + a.own_cap;
+    float4 * lut = reinterpret_cast<float4 *>(oval + a.own_cap);
+    uint32_t * vlist = reinterpret_cast<uint32_t *>(lut + 16);  // [list_cap] allowed vectors of a sparse slice
+    uint32_t * tkey = vlist + a.list_cap;                       // [TS] in-slice offsets whose occurrences are counted
+    uint32_t * tcnt = tkey + TS;                                // [TS]
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(tcnt + TS);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
     const uint32_t id0 = (uint32_t) (a.id_base + lo);
 
     FNS_PHASE_BEGIN
-#ifdef FNS_PHASE_TIMING
-    if (k == 12345) atomicExch(a.err, 3);  // consumes the parameters: phase 10 = their arrival
-    FNS_PHASE(10)
-#endif
-    // The first history ids are requested before anything else: their addresses do not depend on the row's
-    // history length, which is itself still in flight.
-    const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
-    const bool use_hist = any_pen && a.ht_size > 0 && n_s > 0;
+    // Everything whose address is known is requested before anything is waited for: the row's parameters, its
+    // history length, the first history ids and the mask words.
     const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
     const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
+    fns_b200_params p = a.params ? a.params[win] : a.p0;
+    int n_hist = (a.history && a.history_len) ? a.history_len[win] : 0;
     int32_t ids0[4] = {-1, -1, -1, -1};
-    if (use_hist && hrow) {
+    if (hrow && a.own_cap > 0) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int j = u * NT + tid;
             if (j < (int) a.history_stride) ids0[u] = hrow[j];
         }
     }
-    int n_hist = 0;
-    if (a.history && a.history_len) {
-        n_hist = a.history_len[win];
-        n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
-    }
-    const int n_pen = n_hist + (a.draft ? col : 0);
 
     // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
-    // streaming loop needs no bounds handling.  A warp's 32 words lie in one epoch: the epochs that have any
-    // allowed element are collected in sh.epoch_mask, the others are never visited.
+    // streaming loop needs no bounds handling.  Every warp also counts the vectors that have an allowed element
+    // and notes which epochs have any; the block adds these up after the barrier, without atomics.
+    auto vector_units = [](uint32_t m) -> uint32_t {  // one bit per vector: the OR of its mask bits
+        if constexpr (VEC == 1) return m;
+        if constexpr (VEC == 4) return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x11111111u;
+        m |= m >> 4;
+        return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
+    };
     if (tid == 0) {
         sh.n_cand = 0u;
         sh.thr_key = 0ull;
-        sh.epoch_mask = 0u;
-        sh.n_list = 0u;
-        sh.n_stash = 0u;
-        sh.n_av = 0u;
+        sh.n_own = 0u;
         sh.n_vl = 0u;
     }
-    if (tid < kWarps) sh.warp_bound[tid] = 0u;
+    for (int i = tid; i < TS; i += NT) {
+        tkey[i] = kNoKey;
+        tcnt[i] = 0u;
+    }
+    if (tid < 16) {  // addend per mask nibble: 0 keeps an element, -inf removes it from every maximum
+        lut[tid] = make_float4((tid & 1) ? 0.0f : -INFINITY, (tid & 2) ? 0.0f : -INFINITY, (tid & 4) ? 0.0f : -INFINITY,
+                               (tid & 8) ? 0.0f : -INFINITY);
+    }
     {
-        int4 * h4 = reinterpret_cast<int4 *>(hoff);  // offsets empty, counts (the array behind them) zero
-        for (int i = tid; i < a.ht_size / 2; i += NT) {
-            const int fill = i < a.ht_size / 4 ? kHashEmpty : 0;
-            h4[i] = make_int4(fill, fill, fill, fill);
+        const int words = (n_s + 31) >> 5;
+        uint32_t cnt = 0u, epm = 0u;
+        for (int w0 = 0; w0 < a.slice_len / 32; w0 += NT * MW) {
+            uint32_t m[MW];
+#pragma unroll
+            for (int u = 0; u < MW; ++u) {  // independent loads, all in flight together
+                const int w = w0 + u * NT + tid;
+                m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < MW; ++u) {
+                const int w = w0 + u * NT + tid;
+                if (w >= a.slice_len / 32) continue;
+                if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
+                eff[w] = m[u];
+                cnt += (uint32_t) __popc(vector_units(m[u]));
+                if (m[u]) epm |= 1u << (w / (kEpoch / 32));
+            }
+        }
+        cnt = __reduce_add_sync(kFull, cnt);
+        epm = __reduce_or_sync(kFull, epm);
+        if (lane == 0) {
+            sh.red_cnt[warp] = cnt;
+            sh.red_ep[warp] = epm;
         }
     }
-    __syncthreads();
-    const int words = (n_s + 31) >> 5;
-    for (int w0 = 0; w0 < a.slice_len / 32; w0 += NT * 4) {  // slice_len / 32 is a multiple of NT / 2
-        uint32_t m[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {  // four independent loads in flight
-            const int w = w0 + u * NT + tid;
-            m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int w = w0 + u * NT + tid;
-            if (w >= a.slice_len / 32) continue;  // uniform per warp: NT / 2 divides slice_len / 32
-            if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
-            eff[w] = m[u];
-            if (__any_sync(kFull, m[u] != 0u) && lane == 0) atomicOr(&sh.epoch_mask, 1u << (w / (kEpoch / 32)));
-        }
-    }
+    const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
+    const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
+    const bool use_hist = any_pen && a.own_cap > 0 && n_s > 0;
+    n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
+    const int n_pen = n_hist + (a.draft ? col : 0);
     uint64_t best = 0ull;      // k == 1: this thread's best key
     uint32_t lost = 0u;        // elements of the current round that found the buffer full
-    float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    bool hv_ok[4] = {false, false, false, false};
-    FNS_MARK(0)
-#ifdef FNS_PHASE_TIMING
-    if (ids0[0] == 0x7ffffff0 || n_hist == 0x7ffffff0) atomicExch(a.err, 3);  // consumes the prefetched ids
-    FNS_MARK(11)
-#endif
+    __syncthreads();
+    FNS_PHASE(0)
+    int n_av = 0;              // vectors with an allowed element, before the history is taken out
+    uint32_t todo = 0u;        // epochs with an allowed element
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        n_av += (int) sh.red_cnt[w];
+        todo |= sh.red_ep[w];
+    }
 
-    // 2. Penalties.  The row's history (plus the draft prefix of a verification column) is scattered into a
-    // shared hash table: in-slice offset -> occurrence count; the thread that claims a slot also appends it to
-    // a list, so the distinct ids can be walked densely afterwards.  Each distinct id then leaves the bit set
-    // (whether the mask allowed it is kept in bit 30 of its list entry), so the streaming passes pay nothing for
-    // penalties; its penalised value is offered as a candidate after pass 1, when a bound exists that most of
-    // them fail.  Traffic: 4 bytes per history id (every slice reads the list; it stays in L2).
+    // 2. Penalties.  Every history id (plus the draft prefix of a verification column) that lies in the slice
+    // clears its bit in the bit set, so the streaming pass never sees it and pays nothing for penalties.  The
+    // thread that finds the bit still set owns the id: ids that the mask excludes have no owner, and of several
+    // occurrences of one id exactly one thread wins.  Owners append the id to a list (one reservation per warp
+    // and round) and start an asynchronous copy of its logit into shared memory; its penalised value is offered
+    // as a candidate after pass 1, when a bound exists that most of them fail.  The occurrence count (frequency
+    // penalty) is looked up only for the few that could pass the bound.  Traffic: 4 bytes per history id (every
+    // slice reads the list; it stays in L2).
+    int n_own = 0;
     if (use_hist && n_pen > 0) {
-        const uint32_t hmask = (uint32_t) a.ht_size - 1u;
+        const uint32_t below = (1u << lane) - 1u;
         for (int j0 = 0; j0 < n_pen; j0 += NT * 4) {
             int32_t ids[4];
 #pragma unroll
@@ -435,75 +491,45 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 if (j0 == 0 && hrow) ids[u] = j < n_hist ? ids0[u] : (j < n_pen ? drow[j - n_hist] : -1);
                 else ids[u] = j < n_hist ? hrow[j] : (j < n_pen ? drow[j - n_hist] : -1);
             }
+            uint32_t offs[4], pre[4], total = 0u;
+            bool mine[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const uint32_t off = (uint32_t) (ids[u] - a.id_base - lo);
-                if (off >= (uint32_t) n_s || ids[u] < a.id_base) continue;
-                // double hashing: with linear probing the clusters at load 1/2 make the slowest lane of a warp walk
-                // dozens of slots, each a dependent shared-memory access
-                uint32_t h = (off * 2654435761u) >> a.ht_shift;
-                const uint32_t step = ((off * 0x85EBCA6Bu) >> a.ht_shift) | 1u;
-                for (int probe = 0; probe <= a.ht_size; ++probe) {
-                    if (probe == a.ht_size) { atomicExch(a.err, 2); break; }  // table full: cannot happen (load <= 1/2)
-                    int cur = hoff[h];
-                    if (cur == kHashEmpty) cur = atomicCAS(&hoff[h], kHashEmpty, (int) off);  // the old value
-                    if (cur == kHashEmpty || (uint32_t) cur == off) {
-                        const bool claimed = cur == kHashEmpty;
-#ifndef FNS_DBG_NOCNT
-                        atomicAdd(&hcnt[h], 1u);
-#endif
-#ifdef FNS_DBG_NOLIST
-                        if (false) {
-#else
-                        if (claimed) {
-#endif
-                            const cooperative_groups::coalesced_group cg = cooperative_groups::coalesced_threads();
-                            uint32_t base = 0u;
-                            if (cg.thread_rank() == 0) base = atomicAdd(&sh.n_list, cg.size());
-                            hlist[cg.shfl(base, 0) + cg.thread_rank()] = (int) h;
-                        }
-                        break;
-                    }
-                    h = (h + step) & hmask;
+                offs[u] = (uint32_t) (ids[u] - a.id_base - lo);
+                mine[u] = false;
+                if (offs[u] < (uint32_t) n_s && ids[u] >= a.id_base) {
+                    const uint32_t bit = 1u << (offs[u] & 31);
+                    // (the plain read first: excluded ids and repeats, the common case under a mask, cost no atomic)
+                    if (*(volatile uint32_t *) &eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
                 }
+                const uint32_t b = __ballot_sync(kFull, mine[u]);
+                pre[u] = total + (uint32_t) __popc(b & below);
+                total += (uint32_t) __popc(b);
             }
-        }
-        __syncthreads();
-        FNS_PHASE(8)
-        const int n_list = (int) sh.n_list;
-        for (int j = tid; j < n_list; j += NT) {
-            const int h = hlist[j];
-            const uint32_t off = (uint32_t) hoff[h];
-            const uint32_t bit = 1u << (off & 31);
-            if (atomicAnd(&eff[off >> 5], ~bit) & bit) hlist[j] = h | (1 << 30);
-        }
-        FNS_MARK(9)
-        // the logits of the first ids of the list are requested now and parked in shared memory once the first
-        // epochs of pass 1 are in flight, so that nobody waits for them
+            if (total == 0u) continue;  // uniform per warp
+            uint32_t base = 0u;
+            if (lane == 0) base = atomicAdd(&sh.n_own, total);
+            base = __shfl_sync(kFull, base, 0);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int j = u * NT + tid;
-            hv_ok[u] = j < n_list && (hlist[j] & (1 << 30));
-            if (hv_ok[u]) hv[u] = to_float(x[hoff[hlist[j] & ~(1 << 30)]]);
+            for (int u = 0; u < 4; ++u) {
+                if (!mine[u]) continue;
+                own[base + pre[u]] = offs[u];
+                copy_word_async(&oval[base + pre[u]], word_of(x + offs[u]));
+            }
         }
     }
     __syncthreads();
-    // The row's ragged end: the elements of a last, partial vector are taken here one by one and removed from
-    // the bit set, so that the vector loads below never reach past the row.
+    if (use_hist) n_own = (int) sh.n_own;
+    // The row's ragged end: the elements of a last, partial vector are taken out of the bit set here, so that the
+    // vector loads below never reach past the row; each becomes a key that is offered with the other candidates.
+    uint64_t rag_key = 0ull;
     if (VEC > 1 && (n_s % VEC) != 0) {
         if (tid < (n_s % VEC)) {
             const int e = n_s - (n_s % VEC) + tid;
             const uint32_t bit = 1u << (e & 31);
             if (atomicAnd(&eff[e >> 5], ~bit) & bit) {
                 const float xi = to_float(x[e]);
-                if (is_finite(xi)) {
-                    const uint64_t key = make_key(xi, id0 + (uint32_t) e);
-                    if (k == 1) {
-                        best = key > best ? key : best;
-                    } else if (!push(key, buf, sh, a.cap)) {
-                        atomicExch(a.err, 1);  // cannot happen: the buffer is empty here
-                    }
-                }
+                if (is_finite(xi)) rag_key = make_key(xi, id0 + (uint32_t) e);
             }
         }
         __syncthreads();
@@ -512,44 +538,25 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
 
     // 3. Pass 1 over the slice: maxima only.  An epoch gives every thread NV vectors (16 elements); two epochs
     // are in flight (the loads of the next one are issued before the current one is reduced); a vector whose
-    // elements the bit set excludes is not loaded.  Every thread keeps the maximum of what it has seen, and a
-    // 64-bit flag word marks the vector groups whose maximum reaches the running bound.  The bound needs no
-    // buffer: if r = ceil(k / warps) lanes of EVERY warp hold a maximum >= v, the slice has at least k elements
-    // >= v, so nothing below v can be among its best k.  Each warp finds its r-th largest lane maximum with r
-    // warp-wide max reductions and publishes it; the bound is the minimum over the warps (for k = 1: the
-    // maximum).  It is refreshed after epochs 1, 2, 4, 8, 16 and once more at the end.
+    // elements the bit set excludes is not loaded.  Excluded elements of a loaded vector get -inf added (a table
+    // lookup by the vector's mask nibble), so the maxima need no branches.  Every thread keeps the maximum of
+    // what it has seen; a vector group whose maximum reaches the running bound sets a flag bit and is read again
+    // in pass 2.  The bound needs no buffer: if r lanes of EVERY warp hold a maximum >= v (r * warps >= k), the
+    // slice has at least k elements >= v, so nothing below v can be among its best k.  A warp splits into r
+    // groups of lanes (r a power of two), takes each group's maximum and publishes the smallest of them: r
+    // different lanes have reached it.  The bound is the minimum over the warps (for k = 1: the maximum).  It is
+    // refreshed after epochs 1, 2, 4, 8, 16 and once more at the end.
     const uint32_t * effp = eff + ((tid * VEC) >> 5);
     const int bshift = (tid * VEC) & 31;
     const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
     const bool bounded = r_need <= 32;             // otherwise every group is flagged
+    int lanes_per_group = 32;                      // 32 / (r_need rounded up to a power of two)
+    while (lanes_per_group > 1 && (32 / lanes_per_group) < r_need) lanes_per_group >>= 1;
     float tmax = -INFINITY;                        // this thread's maximum so far
-    float thr_v = -FLT_MAX;                        // the bound as a float: x < thr_v cannot be a candidate
-    uint32_t thr_word = 0u;
-    uint64_t flags = 0ull;
+    float thr_v = -FLT_MAX;                        // the bound: x < thr_v cannot be a candidate
+    uint64_t f0 = 0ull, f1 = 0ull;                 // flag bit ep * FPE + g: group g of epoch ep reached the bound
     int done = 0;
 
-    auto refresh = [&]() {  // all threads of the warp
-        uint32_t v = tmax > -INFINITY ? order_word(tmax) : 0u, bound = 0u;
-        int cnt = 0;
-        while (cnt < r_need) {
-            const uint32_t m = __reduce_max_sync(kFull, v);
-            if (m == 0u) { bound = 0u; break; }
-            cnt += __popc(__ballot_sync(kFull, v == m));
-            if (v == m) v = 0u;
-            bound = m;
-        }
-        if (lane == 0) *(volatile uint32_t *) &sh.warp_bound[warp] = bound;
-    };
-    auto read_bound = [&]() {
-        const volatile uint32_t * wb = sh.warp_bound;
-        uint32_t b = wb[0];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) b = k == 1 ? max(b, wb[w]) : min(b, wb[w]);
-        if (b > thr_word) {
-            thr_word = b;
-            thr_v = word_value(b < 0x00800000u ? 0x00800000u : b);
-        }
-    };
     auto issue = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -558,74 +565,61 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
     };
     auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
-        float vmx[NV];
+        float vmx[NV], emax = -INFINITY;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            vmx[i] = mb[i] ? vector_max<VEC>(xv[i], mb[i]) : -INFINITY;
-            tmax = fmaxf(tmax, vmx[i]);
-        }
-        if (bounded && (done & (done + 1)) == 0) {  // done = 0, 1, 3, 7, 15
-            refresh();
-            if (done == 0) __syncthreads();  // the first bound needs every warp's share
-            read_bound();
-        }
-        ++done;
+            float m = -INFINITY;
+            if constexpr (VEC == 1) {
+                m = mb[i] ? xv[i][0] : -INFINITY;
+            } else {
+                // a vector that was not loaded holds stale values: stale - inf is -inf or NaN, and NaN never wins
 #pragma unroll
-        for (int g = 0; g < FPE; ++g) {
-            uint32_t q = 0u;  // the vectors of this group that reach the bound
-#pragma unroll
-            for (int u = 0; u < VPF; ++u) q |= (vmx[g * VPF + u] >= thr_v ? 1u : 0u) << u;
-            if (!q) continue;
-            // Their values go to the stash (pass 2 then needs no memory access).  The group's slots are reserved
-            // together: if they do not all fit, none is used (the reserved ones are marked void) and the flag of
-            // the group makes pass 2 read it again, so no element can be offered twice.
-            const uint32_t want = (uint32_t) __popc(q);
-            uint32_t slot = atomicAdd(&sh.n_stash, want);
-            const bool fits = slot + want <= (uint32_t) a.stash_cap;
-            if (!fits) flags |= 1ull << (ep * FPE + g);
-#pragma unroll
-            for (int u = 0; u < VPF; ++u) {
-                if (!((q >> u) & 1u)) continue;
-                const int i = g * VPF + u;
-                if (fits) {
-                    float4 * dst = reinterpret_cast<float4 *>(stash_val + (size_t) slot * (VEC < 4 ? 4 : VEC));
-                    if constexpr (VEC == 1) {
-                        dst[0] = make_float4(xv[i][0], 0.0f, 0.0f, 0.0f);
-                    } else {
-#pragma unroll
-                        for (int w4 = 0; w4 < VEC / 4; ++w4)
-                            dst[w4] = make_float4(xv[i][4 * w4], xv[i][4 * w4 + 1], xv[i][4 * w4 + 2], xv[i][4 * w4 + 3]);
-                    }
-                    stash_tag[slot] = (uint32_t) (ep * NV + i) | ((uint32_t) tid << 9) | (mb[i] << 18);
-                } else if (slot < (uint32_t) a.stash_cap) {
-                    stash_tag[slot] = 0xffffffffu;  // void
+                for (int q = 0; q < VEC / 4; ++q) {
+                    const float4 t = lut[(mb[i] >> (4 * q)) & 15u];
+                    m = fmaxf(m, fmaxf(fmaxf(xv[i][4 * q] + t.x, xv[i][4 * q + 1] + t.y),
+                                       fmaxf(xv[i][4 * q + 2] + t.z, xv[i][4 * q + 3] + t.w)));
                 }
-                ++slot;
             }
+            vmx[i] = m;
+            emax = fmaxf(emax, m);
+        }
+        constexpr int EPW = 64 / FPE;  // epochs per flag word
+        if (__builtin_expect(!(emax <= FLT_MAX), 0)) {
+            // +inf among the allowed elements: never a candidate (src/kernels.cu:629-639).  The epoch is left to
+            // pass 2, which looks at every element, and adds nothing to this thread's maximum.
+            const uint64_t every = (1ull << FPE) - 1ull;
+            if (ep < EPW) f0 |= every << (ep * FPE);
+            else f1 |= every << ((ep - EPW) * FPE);
+            emax = -INFINITY;
+        }
+        tmax = fmaxf(tmax, emax);
+#ifdef FNS_X_NOREFRESH
+        if (bounded && done == 0)
+#else
+        if (__builtin_expect(bounded && (done & (done + 1)) == 0, 0))  // done = 0, 1, 3, 7, 15
+#endif
+            thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, done == 0, k == 1, sh);
+        ++done;
+        if (__builtin_expect(emax >= thr_v, 0)) {
+            uint64_t hb = 0ull;  // the groups of this epoch that reach the bound
+#pragma unroll
+            for (int g = 0; g < FPE; ++g) {
+                bool q = false;
+#pragma unroll
+                for (int u = 0; u < VPF; ++u) q = q || vmx[g * VPF + u] >= thr_v;
+                hb |= (q ? 1ull : 0ull) << g;
+            }
+            if (ep < EPW) f0 |= hb << (ep * FPE);
+            else f1 |= hb << ((ep - EPW) * FPE);
         }
     };
-    // How many vectors of the slice have an allowed element?  (One bit per vector: the OR of its mask bits.)
-    auto vector_units = [](uint32_t m) -> uint32_t {
-        if constexpr (VEC == 1) return m;
-        if constexpr (VEC == 4) return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x11111111u;
-        m |= m >> 4;
-        return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
-    };
-    {
-        uint32_t cnt = 0u;
-        for (int w = tid; w < a.slice_len / 32; w += NT) cnt += (uint32_t) __popc(vector_units(eff[w]));
-        cnt = __reduce_add_sync(kFull, cnt);
-        if (lane == 0 && cnt) atomicAdd(&sh.n_av, cnt);
-    }
-    __syncthreads();
     constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
-    const int n_av = (int) sh.n_av;
+    const uint32_t epochs = todo;          // (the loop below consumes `todo`)
     const bool sparse = n_av <= min(NT * LPT, a.list_cap);
     if (sparse) {
         // 3a. Few allowed vectors (a grammar mask that admits little): no epochs.  The allowed vectors are listed
         // from the bit set, every thread requests all of its (at most LPT) at once, and after ONE memory round
         // trip the bound is known and the candidates are appended straight from registers.
-        uint32_t * vlist = stash_tag;  // the stash is not used on this path
         for (int w = tid; w < a.slice_len / 32; w += NT) {
             uint32_t t = vector_units(eff[w]);
             if (!t) continue;
@@ -633,6 +627,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             for (; t; t &= t - 1u) vlist[at++] = (uint32_t) (w * (32 / VEC) + (__ffs(t) - 1) / VEC);
         }
         __syncthreads();
+        const int n_vl = (int) sh.n_vl;  // <= n_av: the history took some out
         float xv[LPT][VEC];
         uint32_t mb[LPT];
         int ev[LPT];
@@ -641,16 +636,11 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             const int j = u * NT + tid;
             mb[u] = 0u;
             ev[u] = 0;
-            if (j < n_av) {
+            if (j < n_vl) {
                 ev[u] = (int) vlist[j] * VEC;
                 mb[u] = (eff[ev[u] >> 5] >> (ev[u] & 31)) & kVecBits;
                 load_vec<T, VEC>(x + ev[u], xv[u]);
             }
-        }
-        {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (hv_ok[u]) hval[u * NT + tid] = hv[u];
         }
         float vmx[LPT];
 #pragma unroll
@@ -658,13 +648,9 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             vmx[u] = mb[u] ? vector_max<VEC>(xv[u], mb[u]) : -INFINITY;
             tmax = fmaxf(tmax, vmx[u]);
         }
-        if (bounded) {
-            refresh();
-            __syncthreads();
-            read_bound();
-        }
+        if (bounded) thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, true, k == 1, sh);
         done = 1;
-        const uint64_t tk0 = (uint64_t) thr_word << 32;
+        const uint64_t tk0 = (uint64_t) order_word(thr_v) << 32;
 #pragma unroll
         for (int u = 0; u < LPT; ++u) {
             if (!(vmx[u] >= thr_v)) continue;
@@ -696,10 +682,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 if (!__syncthreads_or(lost != 0u)) break;
             }
         }
-        __syncthreads();
-    } else
-    {
-        uint32_t todo = sh.epoch_mask;  // the same for every thread: read after the barrier above
+    } else {
         auto next = [&]() -> int {
             if (!todo) return -1;
             const int ep = __ffs(todo) - 1;
@@ -707,226 +690,239 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             return ep;
         };
         float xa[NV][VEC], xb[NV][VEC];
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
         uint32_t ma[NV], mb[NV];
         int ea = next(), eb = -1;
         if (ea >= 0) issue(ea, xa, ma);
-        bool parked = false;
+#ifdef FNS_PHASE_TIMING  // thread 0: cycles spent issuing, waiting for the data, reducing
+#define FNS_T_ISSUE(e, xs, ms) { const long long c0 = clock64(); issue(e, xs, ms); if (tid == 0) atomicAdd(&g_phase[14], (unsigned long long) (clock64() - c0)); }
+#define FNS_T_REDUCE(e, xs, ms) { const long long c0 = clock64(); asm volatile("" ::"f"(xs[0][0]), "f"(xs[NV - 1][0])); \
+        const long long c1 = clock64(); reduce(e, xs, ms); const long long c2 = clock64(); \
+        if (tid == 0) { atomicAdd(&g_phase[12], (unsigned long long) (c1 - c0)); atomicAdd(&g_phase[13], (unsigned long long) (c2 - c1)); } }
+#else
+#define FNS_T_ISSUE(e, xs, ms) issue(e, xs, ms);
+#define FNS_T_REDUCE(e, xs, ms) reduce(e, xs, ms);
+#endif
         while (ea >= 0) {
             eb = next();
-            if (eb >= 0) issue(eb, xb, mb);
-            if (!parked) {
-                parked = true;
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (hv_ok[u]) hval[u * NT + tid] = hv[u];
-            }
-            reduce(ea, xa, ma);
+            if (eb >= 0) FNS_T_ISSUE(eb, xb, mb)
+            FNS_T_REDUCE(ea, xa, ma)
             if (eb < 0) break;
             ea = next();
-            if (ea >= 0) issue(ea, xa, ma);
-            reduce(eb, xb, mb);
+            if (ea >= 0) FNS_T_ISSUE(ea, xa, ma)
+            FNS_T_REDUCE(eb, xb, mb)
         }
     }
-    if (done == 0) {  // no epoch had an allowed element: the parked logits were not stored yet
+    copy_word_wait();  // this thread's logit copies have landed; the barrier below shows them to the others
+    const uint32_t wt = tmax > -INFINITY ? order_word(tmax) : 0u;  // this thread's maximum as an order word
+    if (bounded && done > 0) {
+        const uint32_t top = __reduce_max_sync(kFull, wt);
+        if (lane == 0) sh.warp_top[warp] = top;
+        thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
+        // The bound is now tightened to (nearly) the k-th largest of the threads' maxima: k threads that have
+        // reached a value are k elements that have, and a count over the block is one barrier.  The search runs
+        // bit by bit below the highest bit in which the bound so far and the block's maximum differ.
+        if (k > 1 && k <= NT) {
+            uint32_t hi_w = sh.warp_top[0];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (hv_ok[u]) hval[u * NT + tid] = hv[u];
-    }
-    if (bounded && done > 1) {  // the final bound (after one epoch the first refresh already is)
-        refresh();
-        __syncthreads();
-        read_bound();
+            for (int w = 1; w < kWarps; ++w) hi_w = max(hi_w, sh.warp_top[w]);
+            const uint32_t lo_w = order_word(thr_v);
+            if (hi_w > lo_w) {
+                const int split = 31 - __clz((int) (lo_w ^ hi_w));
+                uint32_t bw = split == 31 ? 0u : (lo_w & ~((2u << split) - 1u));  // the common prefix: <= lo_w, so valid
+                const int stop = split > 13 ? split - 13 : 0;
+#pragma unroll 1
+                for (int bit = split; bit >= stop; --bit) {
+                    const uint32_t cand = bw | (1u << bit);
+                    if (__syncthreads_count(wt >= cand) >= k) bw = cand;
+                }
+                if (bw > lo_w) thr_v = word_value(bw);
+            }
+        }
     } else {
-        __syncthreads();  // the stash is complete
+        __syncthreads();
     }
+    thr_v += 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
+    if (!(tmax >= thr_v)) f0 = f1 = 0ull;  // nothing of this thread can be a candidate: its flags are void
     FNS_PHASE(2)
 
-    // The penalised candidates: every distinct history id that the mask allowed, with its penalised value,
-    // against the bound (the bound came from the other elements alone, which can only make it lower than the
-    // true k-th best: still a valid bar).  32 list entries per thread between two votes (one `lost` bit each),
-    // four at a time so that their logit loads overlap.
-    uint64_t thr_key = (uint64_t) thr_word << 32;
-    if (use_hist && n_pen > 0) {
-        const int n_list = (int) sh.n_list;
-        auto entry_key = [&](int h, float v) -> uint64_t {  // v: the raw logit; 0 if the result is not finite
-            const float cnt = (float) hcnt[h];
-            // each step rounded on its own: no fused multiply-add
-            v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
-            v = __fsub_rn(v, __fmul_rn(p.frequency, cnt));
-            v = __fsub_rn(v, p.presence);
-            return is_finite(v) ? make_key(v, id0 + (uint32_t) hoff[h]) : 0ull;
-        };
-        for (int j0 = 0; j0 < n_list; j0 += NT * 32) {
-            for (int g = 0; g < 8 && j0 + g * 4 * NT < n_list; ++g) {
-                int h[4];
-                float v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int j = j0 + (g * 4 + u) * NT + tid;
-                    const int e = j < n_list ? hlist[j] : 0;
-                    h[u] = (e & (1 << 30)) ? (e & ~(1 << 30)) : -1;
-                    if (h[u] >= 0) v[u] = j < 4 * NT ? hval[j] : to_float(x[hoff[h[u]]]);
+    // 4. The candidates.  Three sources are compared with the final bound and what passes is appended to the
+    // buffer: the ragged end, the penalised history ids, and the flagged groups of pass 1 (read again).  With the
+    // tightened bound little more than k keys arrive, so the first attempt does not watch the buffer at all: an
+    // append that finds it full is dropped, and the cursor running past the end afterwards says so.  Only then
+    // (many equal values, k near the buffer size) is everything offered again the careful way: every group
+    // flagged, the block voting after every round on whether to compact (which also raises the bar) and
+    // repeating the appends that failed.  A sparse slice has appended from registers already and goes the
+    // careful way at once.
+    uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
+    auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add
+        v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
+        v = __fsub_rn(v, __fmul_rn(p.frequency, cnt));
+        return __fsub_rn(v, p.presence);
+    };
+    auto pop_flag = [&]() -> int {
+        if (f0) {
+            const int b = __ffsll((long long) f0) - 1;
+            f0 &= f0 - 1ull;
+            return b;
+        }
+        if (f1) {
+            const int b = __ffsll((long long) f1) - 1;
+            f1 &= f1 - 1ull;
+            return 64 + b;
+        }
+        return -1;
+    };
+    for (int attempt = sparse ? 1 : 0; attempt < 2; ++attempt) {
+        const bool careful = attempt == 1 && k > 1;
+        // (a) the ragged end
+        if (rag_key != 0ull) {
+            if (k == 1) best = rag_key > best ? rag_key : best;
+            else if (rag_key >= thr_key) push(rag_key, buf, sh, a.cap);  // at most VEC - 1 keys, first in the buffer
+        }
+        // (b) Every owned history id with its penalised value (the bound came from the other elements alone, which
+        // can only make it lower than the true k-th best: still a valid bar).  One list entry per thread and round.
+        // The value with ONE occurrence is computed first; with a frequency penalty >= 0 more occurrences can only
+        // lower it, so an id's occurrences are counted only if that value reaches the bound: such ids enter a
+        // small hash table, the block walks the history once and counts the hits, and the owners read their counts
+        // back (and empty their slots for the next round).
+        if (n_own > 0) {
+            const bool counts = p.frequency != 0.0f;
+            const bool count_all = p.frequency < 0.0f;  // then more occurrences raise the value
+            for (int j0 = 0; j0 < n_own; j0 += NT) {
+                const int j = j0 + tid;
+                uint32_t off = 0u;
+                float raw = 0.0f, v = -INFINITY;
+                bool live = j < n_own;
+                if (live) {
+                    off = own[j];
+                    raw = value_in_word(oval[j], x + off);
+                    v = penalised(raw, 1.0f);
+                    live = count_all || v >= thr_v;
                 }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (h[u] < 0) continue;
-                    const uint64_t key = entry_key(h[u], v[u]);
-                    if (key == 0ull) continue;
+                if (counts && __syncthreads_or(live)) {
+                    uint32_t slot = 0u;
+                    if (live) {  // owned ids are distinct: every insert claims an empty slot
+                        slot = (off * 2654435761u) >> kTShift;
+                        while (atomicCAS(&tkey[slot], kNoKey, off) != kNoKey) slot = (slot + 1u) & (TS - 1);
+                    }
+                    __syncthreads();
+                    for (int t = tid; t < n_pen; t += NT) {
+                        const int32_t id = t < n_hist ? hrow[t] : drow[t - n_hist];
+                        const uint32_t o = (uint32_t) (id - a.id_base - lo);
+                        if (o >= (uint32_t) n_s || id < a.id_base) continue;
+                        uint32_t h = (o * 2654435761u) >> kTShift;
+                        for (uint32_t kx = tkey[h]; kx != kNoKey; kx = tkey[h]) {  // at most NT keys in 2 * NT slots
+                            if (kx == o) {
+                                atomicAdd(&tcnt[h], 1u);
+                                break;
+                            }
+                            h = (h + 1u) & (TS - 1);
+                        }
+                    }
+                    __syncthreads();
+                    if (live) {
+                        v = penalised(raw, (float) tcnt[slot]);
+                        tkey[slot] = kNoKey;
+                        tcnt[slot] = 0u;
+                    }
+                }
+                uint64_t key = 0ull;
+                if (live && is_finite(v)) key = make_key(v, id0 + off);
+                bool full = false;
+                if (key != 0ull) {
                     if (k == 1) best = key > best ? key : best;
-                    else if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (g * 4 + u);
+                    else if (key >= thr_key) full = !push(key, buf, sh, a.cap);
                 }
-            }
-            if (k > 1 && n_list + VEC > a.trigger) {  // uniform: only a long list can fill the buffer
-                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                    compact<NT>(buf, sel, k, a.cap, sh);
-                    const uint64_t tk = sh.thr_key;
-                    if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
-                    uint32_t still = 0u;
-                    for (uint32_t m = lost; m; m &= m - 1u) {
-                        const int b = __ffs(m) - 1;
-                        const int h = hlist[j0 + b * NT + tid] & ~(1 << 30);
-                        const uint64_t key = entry_key(h, to_float(x[hoff[h]]));
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+                if (careful && n_own + VEC > a.trigger) {  // uniform: only a long list can fill the buffer
+                    while (__syncthreads_or(full || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                        compact<NT>(buf, sel, k, a.cap, sh);
+                        const uint64_t tk = sh.thr_key;
+                        if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+                        if (full && (key < thr_key || push(key, buf, sh, a.cap))) full = false;
+                        if (!__syncthreads_or(full)) break;
                     }
-                    lost = still;
-                    if (!__syncthreads_or(lost != 0u)) break;
                 }
             }
         }
-    }
-
-    // Pass 2, first the stash: the vectors that reached the bound when they were streamed, values and all, are
-    // compared with the final bound; what passes is appended.  No memory access, no rounds: the entries are
-    // spread evenly over the threads.
-    {
-        constexpr int SE = VEC < 4 ? 4 : VEC;  // floats per stash entry
-        const int n_st = (int) min(sh.n_stash, (uint32_t) a.stash_cap);
-        // a vote is needed only if the appends could fill the buffer.  The decision must be the same in every
-        // thread, so it uses counts that no longer change here (the append cursor itself is moving): what the
-        // penalty list and the ragged end can have appended at most, plus every stashed element
-        const bool may_fill = (int) sh.n_list + VEC + n_st * VEC > a.trigger;
-        for (int i0 = 0; i0 < n_st; i0 += NT) {
-            const int i = i0 + tid;
-            uint32_t ebase = 0u;
-            const uint32_t tag = i < n_st ? stash_tag[i] : 0xffffffffu;
-            if (tag != 0xffffffffu) {
-                const int vi = (int) (tag & 511u), owner = (int) ((tag >> 9) & 511u);
-                const uint32_t bits = tag >> 18;
-                const int ep = vi / NV, iv = vi - ep * NV;
-                ebase = (uint32_t) ((ep * NT * NV + iv * NT + owner) * VEC);
+        // (c) The flagged groups.  Their vectors go on a work list that the whole block then shares: one vector per
+        // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
+        // careful way walks every epoch instead, one per round, with a vote after each.
+        bool listed = true;
+        if (!careful) {
+            while ((f0 | f1) != 0ull) {
+                const int b = pop_flag();
+                const int ep = b / FPE, g = b - ep * FPE;
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) {
-                    const float xi = stash_val[(size_t) i * SE + j];
-                    if (((bits >> j) & 1u) && xi >= thr_v && xi <= FLT_MAX) {
-                        const uint64_t key = make_key(xi, id0 + ebase + (uint32_t) j);
-                        if (k == 1) best = key > best ? key : best;
-                        else if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << j;
-                    }
+                for (int u = 0; u < VPF; ++u) {
+                    const uint32_t at = atomicAdd(&sh.n_vl, 1u);
+                    if (at < (uint32_t) a.list_cap) vlist[at] = (uint32_t) (ep * NT * NV + (g * VPF + u) * NT + tid);
                 }
             }
-            if (k > 1 && may_fill) {
-                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                    compact<NT>(buf, sel, k, a.cap, sh);
-                    const uint64_t tk = sh.thr_key;
-                    if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
-                    uint32_t still = 0u;
-                    for (uint32_t m = lost; m; m &= m - 1u) {
-                        const int b = __ffs(m) - 1;
-                        const uint64_t key = make_key(stash_val[(size_t) i * SE + b], id0 + ebase + (uint32_t) b);
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
-                    }
-                    lost = still;
-                    if (!__syncthreads_or(lost != 0u)) break;
-                }
-            }
-        }
-    }
-
-    // Pass 2, then the groups that did not fit the stash (none unless the input is adversarial or k is large):
-    // they are read again (from L1 / L2: the slice was just streamed) and their
-    // elements compared with the final bound, up to GPR groups per thread and round, their loads issued
-    // together.  What passes is appended; the block votes once per round on whether to compact (buffer filling
-    // up, or an append that found it full, which is then offered again after the compaction).
-    if (k == 1) {
-        while (flags) {
-            const int b = __ffsll((long long) flags) - 1;
-            flags &= flags - 1ull;
-            const int ep = b / FPE, g = b - ep * FPE;
-#pragma unroll
-            for (int u = 0; u < VPF; ++u) {
-                const int i = g * VPF + u;
-                const int e = (ep * NT * NV + i * NT + tid) * VEC;
-                const uint32_t bits = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+            __syncthreads();
+            const int n_work = (int) sh.n_vl;
+            listed = n_work <= a.list_cap;  // uniform; a list that does not fit sends the slice the careful way
+#pragma unroll 1
+            for (int i = tid; i < n_work && listed; i += NT) {
+                const int e = (int) vlist[i] * VEC;
+                const uint32_t bits = (eff[e >> 5] >> (e & 31)) & kVecBits;
                 if (!bits) continue;
                 float xv[VEC];
                 load_vec<T, VEC>(x + e, xv);
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) {
-                    if (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) {
-                        const uint64_t key = make_key(xv[j], id0 + (uint32_t) (e + j));
-                        best = key > best ? key : best;
-                    }
+                    if (!(((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX)) continue;
+                    const uint64_t key = make_key(xv[j], id0 + (uint32_t) (e + j));
+                    if (k == 1) best = key > best ? key : best;
+                    else if (key >= thr_key) push(key, buf, sh, a.cap);
                 }
             }
-        }
-    } else {
-        while (__syncthreads_or(flags != 0ull)) {
-            int eoff[GPR * VPF];      // element offset of each vector of this round (-1: none)
-            uint32_t bits[GPR * VPF];
-            float xv[GPR * VPF][VEC];
+        } else if (!sparse) {
+#pragma unroll 1
+            for (uint32_t m = epochs; m; m &= m - 1u) {
+                const int ep = __ffs(m) - 1;
+                uint32_t bits[NV], lost = 0u;  // lost: elements of this round that found the buffer full
+                float xv[NV][VEC];
 #pragma unroll
-            for (int q = 0; q < GPR; ++q) {
-                int b = -1;
-                if (flags) {
-                    b = __ffsll((long long) flags) - 1;
-                    flags &= flags - 1ull;
+                for (int i = 0; i < NV; ++i) {
+                    bits[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+                    if (bits[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
                 }
-                const int ep = b / FPE, g = b - ep * FPE;
 #pragma unroll
-                for (int u = 0; u < VPF; ++u) {
-                    const int i = g * VPF + u;
-                    const int v = q * VPF + u;
-                    eoff[v] = -1;
-                    bits[v] = 0u;
-                    if (b >= 0) {
-                        bits[v] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-                        if (bits[v]) {
-                            eoff[v] = (ep * NT * NV + i * NT + tid) * VEC;
-                            load_vec<T, VEC>(x + eoff[v], xv[v]);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int v = 0; v < GPR * VPF; ++v) {
-                if (eoff[v] < 0) continue;
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) {
-                    if (((bits[v] >> j) & 1u) && xv[v][j] >= thr_v && xv[v][j] <= FLT_MAX) {
-                        const uint64_t key = make_key(xv[v][j], id0 + (uint32_t) (eoff[v] + j));
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (v * VEC + j);
-                    }
-                }
-            }
-            while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                compact<NT>(buf, sel, k, a.cap, sh);
-                const uint64_t tk = sh.thr_key;
-                if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
-                uint32_t still = 0u;
-#pragma unroll
-                for (int v = 0; v < GPR * VPF; ++v) {
+                for (int i = 0; i < NV; ++i) {
+                    if (!bits[i]) continue;
 #pragma unroll
                     for (int j = 0; j < VEC; ++j) {
-                        if (!((lost >> (v * VEC + j)) & 1u)) continue;
-                        const int e = eoff[v] + j;
-                        const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << (v * VEC + j);
+                        if (!(((bits[i] >> j) & 1u) && xv[i][j] >= thr_v && xv[i][j] <= FLT_MAX)) continue;
+                        const uint64_t key = make_key(xv[i][j], id0 + (uint32_t) ((ep * NT * NV + i * NT + tid) * VEC + j));
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (i * VEC + j);
                     }
                 }
-                lost = still;
-                if (!__syncthreads_or(lost != 0u)) break;
+                while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
+                    compact<NT>(buf, sel, k, a.cap, sh);
+                    const uint64_t tk = sh.thr_key;
+                    if (tk > thr_key) { thr_key = tk; thr_v = key_floor_value(tk); }
+                    uint32_t still = 0u;
+                    for (uint32_t q = lost; q; q &= q - 1u) {
+                        const int b = __ffs(q) - 1;
+                        const int e = (ep * NT * NV + (b / VEC) * NT + tid) * VEC + (b % VEC);
+                        const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
+                        if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
+                    }
+                    lost = still;
+                    if (!__syncthreads_or(lost != 0u)) break;
+                }
             }
         }
+        __syncthreads();
+        if (attempt == 1 || (listed && (k == 1 || sh.n_cand <= (uint32_t) a.cap))) break;  // uniform: all is in
+        // The buffer or the work list overflowed: start again from an empty buffer, the careful way.
+        __syncthreads();
+        if (tid == 0) sh.n_cand = 0u;
+        __syncthreads();
     }
     __syncthreads();
     FNS_PHASE(3)
@@ -993,6 +989,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     }
     __syncthreads();
     if (!sh.is_last) return;
+    FNS_PHASE(6)
     __threadfence();
     const uint64_t * lists = a.cand + (size_t) row * a.slices * a.k_cap;
     if (k == 1) {  // greedy: the largest of the slices' best keys, no sort, no draw
@@ -1024,7 +1021,9 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         buf[i] = __ldcg(lists + (size_t) l * a.k_cap + j);
     }
     __syncthreads();
+    FNS_PHASE(7)
     const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, sh.sc, k, a.k_cap);
+    FNS_PHASE(9)
     draw_tail<NT>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
     FNS_PHASE(5)
 }
@@ -1134,7 +1133,7 @@ struct fns_b200_sampler {
 namespace {
 
 struct Plan {
-    int threads, slices, slice_len, cap, trigger, ht_size, vec, stash_cap;
+    int threads, slices, slice_len, cap, trigger, own_cap, vec, list_cap;
     size_t smem_select;
 };
 
@@ -1186,17 +1185,12 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     pl.trigger = base_cap / 2;
     pl.cap = base_cap;
     if (pl.slices * k_cap > pl.cap) pl.cap = pl.slices * k_cap;  // room to merge the row's lists
-    pl.ht_size = 0;
-    if (hist_bound > 0) {
-        const int distinct = hist_bound < pl.slice_len ? hist_bound : pl.slice_len;
-        pl.ht_size = next_pow2(2 * distinct);
-        if (pl.ht_size < 1024) pl.ht_size = 1024;
-    }
-    // stash: 16 KB of flagged vectors (tag + max(vec, 4) floats each)
-    const int entry_floats = pl.vec < 4 ? 4 : pl.vec;
-    pl.stash_cap = 16384 / (4 * entry_floats + 4) / 4 * 4;  // a multiple of 4: what follows stays 16-byte aligned
-    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.ht_size * 12 +
-                     (size_t) pl.stash_cap * (4 * entry_floats + 4) + sizeof(SelectShared) + 16;
+    pl.cap = round_up(pl.cap, 2);  // what follows the buffer stays 16-byte aligned
+    pl.own_cap = 0;
+    if (hist_bound > 0) pl.own_cap = round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4);
+    pl.list_cap = pl.threads * 8;  // the sparse path lists at most 8 vectors per thread
+    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.own_cap * 8 +
+                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 16 + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
 
@@ -1301,11 +1295,8 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.slice_len = pl.slice_len;
     a.cap = pl.cap;
     a.trigger = pl.trigger;
-    a.ht_size = pl.ht_size;
-    a.ht_shift = 32;
-    for (int t = pl.ht_size; t > 1; t >>= 1) --a.ht_shift;
-    a.stash_cap = pl.stash_cap;
-    a.list_cap = pl.stash_cap * ((pl.vec < 4 ? 4 : pl.vec) + 1);  // 32-bit words in the stash's memory
+    a.own_cap = pl.own_cap;
+    a.list_cap = pl.list_cap;
     a.cand = s->cand;
     a.tickets = s->tickets;
     a.out_tokens = out_tokens;
