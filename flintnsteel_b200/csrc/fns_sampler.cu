@@ -383,7 +383,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     uint32_t * vlist = reinterpret_cast<uint32_t *>(lut + 16);  // [list_cap] allowed vectors of a sparse slice
     uint32_t * tkey = vlist + a.list_cap;                       // [TS] in-slice offsets whose occurrences are counted
     uint32_t * tcnt = tkey + TS;                                // [TS]
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(tcnt + TS);
+    uint32_t * taint = tcnt + TS;                               // [NT] per thread: its largest history logit
+    uint32_t * notplain = taint + NT;                           // [32] per epoch: warps that must look at the bit set
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(notplain + 32);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
@@ -414,6 +416,13 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         m |= m >> 4;
         return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
     };
+    const int words = (n_s + 31) >> 5;
+    uint32_t m[MW];  // this thread's words of the mask: slice_len / 32 <= NT * MW
+#pragma unroll
+    for (int u = 0; u < MW; ++u) {  // independent loads, all in flight together
+        const int w = u * NT + tid;
+        m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
+    }
     if (tid == 0) {
         sh.n_cand = 0u;
         sh.thr_key = 0ull;
@@ -424,29 +433,28 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         tkey[i] = kNoKey;
         tcnt[i] = 0u;
     }
+    taint[tid] = 0u;
+    if (tid < 32) notplain[tid] = 0u;
     if (tid < 16) {  // addend per mask nibble: 0 keeps an element, -inf removes it from every maximum
         lut[tid] = make_float4((tid & 1) ? 0.0f : -INFINITY, (tid & 2) ? 0.0f : -INFINITY, (tid & 4) ? 0.0f : -INFINITY,
                                (tid & 8) ? 0.0f : -INFINITY);
     }
+    __syncthreads();
     {
-        const int words = (n_s + 31) >> 5;
         uint32_t cnt = 0u, epm = 0u;
-        for (int w0 = 0; w0 < a.slice_len / 32; w0 += NT * MW) {
-            uint32_t m[MW];
 #pragma unroll
-            for (int u = 0; u < MW; ++u) {  // independent loads, all in flight together
-                const int w = w0 + u * NT + tid;
-                m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
-            }
-#pragma unroll
-            for (int u = 0; u < MW; ++u) {
-                const int w = w0 + u * NT + tid;
-                if (w >= a.slice_len / 32) continue;
-                if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
-                eff[w] = m[u];
-                cnt += (uint32_t) __popc(vector_units(m[u]));
-                if (m[u]) epm |= 1u << (w / (kEpoch / 32));
-            }
+        for (int u = 0; u < MW; ++u) {
+            const int w = u * NT + tid;
+            if (w >= a.slice_len / 32) continue;  // uniform per warp: 32 divides slice_len / 32
+            if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
+            eff[w] = m[u];
+            cnt += (uint32_t) __popc(vector_units(m[u]));
+            if (m[u]) epm |= 1u << (w / (kEpoch / 32));
+            // A warp whose words of an epoch are all ones streams that epoch without looking at the bit set.  Word r
+            // of a vector row belongs to the threads r * 32 / VEC ..., that is to warp r / VEC.
+            const uint32_t reader = m[u] != 0xffffffffu ? 1u << ((w % kWordsPerVec) / VEC) : 0u;
+            const uint32_t readers = __reduce_or_sync(kFull, reader);
+            if (lane == 0 && readers) atomicOr(&notplain[w / (kEpoch / 32)], readers);
         }
         cnt = __reduce_add_sync(kFull, cnt);
         epm = __reduce_or_sync(kFull, epm);
@@ -481,6 +489,15 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     // penalty) is looked up only for the few that could pass the bound.  Traffic: 4 bytes per history id (every
     // slice reads the list; it stays in L2).
     int n_own = 0;
+    uint32_t t_base = 0u, t_pre = 0u, t_mine = 0u;  // this thread's list slots of the first round
+    // A history logit may become its thread's maximum in an epoch that is streamed without the bit set.  Such a
+    // maximum must not count as a witness for the bound, so every owner records the logit in taint[] of the thread
+    // that streams the element: a thread whose maximum does not exceed its taint is left out of the bound.
+    auto publish_taint = [&](uint32_t slot) {
+        const uint32_t off = own[slot];
+        const float raw = value_in_word(oval[slot], x + off);
+        if (is_finite(raw)) atomicMax(&taint[(off / VEC) & (NT - 1)], order_word(raw));
+    };
     if (use_hist && n_pen > 0) {
         const uint32_t below = (1u << lane) - 1u;
         for (int j0 = 0; j0 < n_pen; j0 += NT * 4) {
@@ -516,6 +533,16 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 own[base + pre[u]] = offs[u];
                 copy_word_async(&oval[base + pre[u]], word_of(x + offs[u]));
             }
+            if (j0 == 0) {
+                t_base = base;
+                t_pre = pre[0] | (pre[1] << 8) | (pre[2] << 16) | (pre[3] << 24);  // each < 128
+                t_mine = (mine[0] ? 1u : 0u) | (mine[1] ? 2u : 0u) | (mine[2] ? 4u : 0u) | (mine[3] ? 8u : 0u);
+            } else {  // a long history: no point in hiding this latency
+                copy_word_wait();
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (mine[u]) publish_taint(base + pre[u]);
+            }
         }
     }
     __syncthreads();
@@ -545,7 +572,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     // slice has at least k elements >= v, so nothing below v can be among its best k.  A warp splits into r
     // groups of lanes (r a power of two), takes each group's maximum and publishes the smallest of them: r
     // different lanes have reached it.  The bound is the minimum over the warps (for k = 1: the maximum).  It is
-    // refreshed after epochs 1, 2, 4, 8, 16 and once more at the end.
+    // made after the first epoch, refreshed after the fourth, and tightened at the end (flags are cheap: only the
+    // few threads that hold a candidate ever look at theirs).
     const uint32_t * effp = eff + ((tid * VEC) >> 5);
     const int bshift = (tid * VEC) & 31;
     const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
@@ -557,31 +585,54 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     uint64_t f0 = 0ull, f1 = 0ull;                 // flag bit ep * FPE + g: group g of epoch ep reached the bound
     int done = 0;
 
+    uint32_t taint_w = 0u;  // this thread's taint, read when the first bound is made
+    auto clean_max = [&]() -> float { return (tmax > -INFINITY && order_word(tmax) > taint_w) ? tmax : -INFINITY; };
     auto issue = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
+        const bool plain = !((notplain[ep] >> warp) & 1u);  // the same for the whole warp
+        if (plain) {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            mb[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-            if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
-        }
-    };
-    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
-        float vmx[NV], emax = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            float m = -INFINITY;
-            if constexpr (VEC == 1) {
-                m = mb[i] ? xv[i][0] : -INFINITY;
-            } else {
-                // a vector that was not loaded holds stale values: stale - inf is -inf or NaN, and NaN never wins
-#pragma unroll
-                for (int q = 0; q < VEC / 4; ++q) {
-                    const float4 t = lut[(mb[i] >> (4 * q)) & 15u];
-                    m = fmaxf(m, fmaxf(fmaxf(xv[i][4 * q] + t.x, xv[i][4 * q + 1] + t.y),
-                                       fmaxf(xv[i][4 * q + 2] + t.z, xv[i][4 * q + 3] + t.w)));
-                }
+            for (int i = 0; i < NV; ++i) {
+                mb[i] = kVecBits;
+                load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
             }
-            vmx[i] = m;
-            emax = fmaxf(emax, m);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                mb[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
+                if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
+            }
+        }
+        return plain;
+    };
+    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
+        float vmx[NV], emax = -INFINITY;
+        if (plain) {  // every element counts (history ids too: see taint)
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                float m = xv[i][0];
+#pragma unroll
+                for (int j = 1; j < VEC; ++j) m = fmaxf(m, xv[i][j]);
+                vmx[i] = m;
+                emax = fmaxf(emax, m);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                float m = -INFINITY;
+                if constexpr (VEC == 1) {
+                    m = mb[i] ? xv[i][0] : -INFINITY;
+                } else {
+                    // a vector that was not loaded holds stale values: stale - inf is -inf or NaN, and NaN never wins
+#pragma unroll
+                    for (int q = 0; q < VEC / 4; ++q) {
+                        const float4 t = lut[(mb[i] >> (4 * q)) & 15u];
+                        m = fmaxf(m, fmaxf(fmaxf(xv[i][4 * q] + t.x, xv[i][4 * q + 1] + t.y),
+                                           fmaxf(xv[i][4 * q + 2] + t.z, xv[i][4 * q + 3] + t.w)));
+                    }
+                }
+                vmx[i] = m;
+                emax = fmaxf(emax, m);
+            }
         }
         constexpr int EPW = 64 / FPE;  // epochs per flag word
         if (__builtin_expect(!(emax <= FLT_MAX), 0)) {
@@ -596,9 +647,15 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
 #ifdef FNS_X_NOREFRESH
         if (bounded && done == 0)
 #else
-        if (__builtin_expect(bounded && (done & (done + 1)) == 0, 0))  // done = 0, 1, 3, 7, 15
+        if (__builtin_expect(bounded && (done == 0 || done == 3), 0))
 #endif
-            thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, done == 0, k == 1, sh);
+        {
+            if (done == 0 && n_own > 0) {  // uniform: the owners have published their taint before their first reduce
+                __syncthreads();
+                taint_w = taint[tid];
+            }
+            thr_v = block_bound<NT>(clean_max(), thr_v, lanes_per_group, done == 0, k == 1, sh);
+        }
         ++done;
         if (__builtin_expect(emax >= thr_v, 0)) {
             uint64_t hb = 0ull;  // the groups of this epoch that reach the bound
@@ -696,32 +753,35 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
         uint32_t ma[NV], mb[NV];
         int ea = next(), eb = -1;
-        if (ea >= 0) issue(ea, xa, ma);
-#ifdef FNS_PHASE_TIMING  // thread 0: cycles spent issuing, waiting for the data, reducing
-#define FNS_T_ISSUE(e, xs, ms) { const long long c0 = clock64(); issue(e, xs, ms); if (tid == 0) atomicAdd(&g_phase[14], (unsigned long long) (clock64() - c0)); }
-#define FNS_T_REDUCE(e, xs, ms) { const long long c0 = clock64(); asm volatile("" ::"f"(xs[0][0]), "f"(xs[NV - 1][0])); \
-        const long long c1 = clock64(); reduce(e, xs, ms); const long long c2 = clock64(); \
-        if (tid == 0) { atomicAdd(&g_phase[12], (unsigned long long) (c1 - c0)); atomicAdd(&g_phase[13], (unsigned long long) (c2 - c1)); } }
-#else
-#define FNS_T_ISSUE(e, xs, ms) issue(e, xs, ms);
-#define FNS_T_REDUCE(e, xs, ms) reduce(e, xs, ms);
-#endif
+        bool pa = false, pb = false;
+        if (ea >= 0) pa = issue(ea, xa, ma);
+        bool first = true;
         while (ea >= 0) {
             eb = next();
-            if (eb >= 0) FNS_T_ISSUE(eb, xb, mb)
-            FNS_T_REDUCE(ea, xa, ma)
+            if (eb >= 0) pb = issue(eb, xb, mb);
+            if (first) {  // with two epochs requested: the history logits of this thread's ids, for the taint
+                first = false;
+                if (t_mine) {
+                    copy_word_wait();
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if ((t_mine >> u) & 1u) publish_taint(t_base + ((t_pre >> (8 * u)) & 255u));
+                }
+            }
+            reduce(ea, xa, ma, pa);
             if (eb < 0) break;
             ea = next();
-            if (ea >= 0) FNS_T_ISSUE(ea, xa, ma)
-            FNS_T_REDUCE(eb, xb, mb)
+            if (ea >= 0) pa = issue(ea, xa, ma);
+            reduce(eb, xb, mb, pb);
         }
     }
     copy_word_wait();  // this thread's logit copies have landed; the barrier below shows them to the others
-    const uint32_t wt = tmax > -INFINITY ? order_word(tmax) : 0u;  // this thread's maximum as an order word
+    const float cmax = clean_max();
+    const uint32_t wt = cmax > -INFINITY ? order_word(cmax) : 0u;  // this thread's witness as an order word
     if (bounded && done > 0) {
         const uint32_t top = __reduce_max_sync(kFull, wt);
         if (lane == 0) sh.warp_top[warp] = top;
-        thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
+        thr_v = block_bound<NT>(cmax, thr_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
         // The bound is now tightened to (nearly) the k-th largest of the threads' maxima: k threads that have
         // reached a value are k elements that have, and a count over the block is one barrier.  The search runs
         // bit by bit below the highest bit in which the bound so far and the block's maximum differ.
@@ -1190,7 +1250,7 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     if (hist_bound > 0) pl.own_cap = round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4);
     pl.list_cap = pl.threads * 8;  // the sparse path lists at most 8 vectors per thread
     pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.own_cap * 8 +
-                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 16 + sizeof(SelectShared) + 16;
+                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + 128 + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
 
