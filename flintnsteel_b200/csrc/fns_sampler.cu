@@ -38,12 +38,16 @@
 namespace fnsb {
 
 #ifdef FNS_PHASE_TIMING  // development aid: block time per phase, summed over blocks (thread 0's clock)
-__device__ unsigned long long g_phase[16];
-#define FNS_PHASE_BEGIN long long ph_t = clock64();
+__device__ unsigned long long g_phase[32];  // [0, 16): sums over blocks; [16, 32): maxima over blocks
+__device__ unsigned g_rowphase[1024][16];   // last launch: cycles per phase of the blocks (blockIdx.y, slice 0)
+#define FNS_PHASE_BEGIN long long ph_t = clock64(); const long long ph_0 = ph_t;
 #define FNS_PHASE(i)                                                           \
     if (threadIdx.x == 0) {                                                    \
         const long long ph_n = clock64();                                      \
         atomicAdd(&g_phase[i], (unsigned long long) (ph_n - ph_t));            \
+        atomicMax(&g_phase[16 + i], (unsigned long long) (ph_n - ph_t));       \
+        atomicMax(&g_phase[16 + 15], (unsigned long long) (ph_n - ph_0));      \
+        if (blockIdx.x == 0 && blockIdx.y < 1024) { g_rowphase[blockIdx.y][i] = (unsigned) (ph_n - ph_t); g_rowphase[blockIdx.y][15] = (unsigned) (ph_n - ph_0); } \
         ph_t = ph_n;                                                           \
     }
 #define FNS_MARK(i) __syncthreads(); FNS_PHASE(i)
@@ -160,63 +164,76 @@ __device__ void compact(uint64_t * buf, uint64_t * sel, int k, int cap, SelectSh
 }
 
 // `lists` lists of `len` keys each in buf, every list sorted in the total order with its empty slots (0) at the
-// end, merged into sorted[0 .. k): the selection rounds of k_sample (src/kernels.cu:680-695).  With few lists
-// every key is ranked directly (its position plus, by binary search, the number of larger keys in each other
-// list; no barrier), else by radix selection.  Returns the number of candidates (< k when fewer tokens are
-// allowed, src/kernels.cu:698-699); sorted[nk .. k_cap) = 0.  All NT threads; block synchronised on entry and
-// exit.
+// end, merged into sorted[0 .. k): the selection rounds of k_sample (src/kernels.cu:680-695).  Returns the number
+// of candidates (< k when fewer tokens are allowed, src/kernels.cu:698-699); sorted[nk .. k_cap) = 0.
+//   1. Witnesses: the first few keys of every list, at least k in all.  The k-th largest witness (found by
+//      counting, every witness against every other) is a bar that k keys reach, so the best k keys of the union
+//      all reach it.
+//   2. Every key that reaches the bar moves to a scratch list (`spare`, room for spare_len keys).  The lists are
+//      sorted, so these are a prefix of each: little more than k keys unless one list holds most of the best.
+//   3. The scratch list is ranked by counting; ranks below k are the answer, in order.
+// If there are too few witnesses or the scratch list overflows, a radix selection over all keys does the job.
+// All NT threads; block synchronised on entry and exit.
 template <int NT>
-__device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, uint64_t * sorted, SelectScratch & sc,
-                           int k, int k_cap) {
+__device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, uint64_t * sorted, uint64_t * spare,
+                           int spare_len, SelectScratch & sc, int k, int k_cap) {
     const int tid = threadIdx.x;
     const int total = lists * len;
+    int depth = (k + lists - 1) / lists + 2;
+    if (depth > len) depth = len;
+    const int n_wit = lists * depth;
+    for (int j = tid; j < k_cap; j += NT) sorted[j] = 0ull;
+    if (tid == 0) {
+        sc.count = 0u;
+        sc.or_hi = 0u;  // the bar, as two words
+        sc.or_lo = 0u;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_wit; i += NT) {
+        const uint64_t key = buf[(i / depth) * len + (i % depth)];
+        if (key == 0ull) continue;
+        int rank = 0;
+        for (int l = 0; l < lists; ++l)
+            for (int d = 0; d < depth; ++d) rank += buf[l * len + d] > key ? 1 : 0;
+        if (rank == k - 1) {
+            sc.or_hi = (uint32_t) (key >> 32);
+            sc.or_lo = (uint32_t) key;
+        }
+    }
+    __syncthreads();
+    const uint64_t bar = ((uint64_t) sc.or_hi << 32) | sc.or_lo;  // 0: fewer than k witnesses
+    for (int i = tid; i < total; i += NT) {
+        const uint64_t key = buf[i];
+        if (key != 0ull && key >= bar) {
+            const uint32_t at = atomicAdd(&sc.count, 1u);
+            if (at < (uint32_t) spare_len) spare[at] = key;
+        }
+    }
+    __syncthreads();
+    const int n = (int) sc.count;
     int nk;
-    if (lists <= 8) {
-        for (int j = tid; j < k_cap; j += NT) sorted[j] = 0ull;
-        if (tid == 0) sc.count = 0u;
+    if (n <= spare_len) {
+        nk = block_rank_select<NT>(spare, n, k, sorted);
         __syncthreads();
-        int mine = 0;
-        for (int i = tid; i < total; i += NT) {
-            const uint64_t key = buf[i];
-            if (key == 0ull) continue;
-            ++mine;
-            const int l = i / len;
-            int rank = i - l * len;
-            for (int o = 0; o < lists && rank < k; ++o) {
-                if (o == l) continue;
-                const uint64_t * other = buf + o * len;
-                int lo = 0, hi = len;  // number of keys of `other` that are larger (it is sorted descending)
-                while (lo < hi) {
-                    const int mid = (lo + hi) >> 1;
-                    if (other[mid] > key) lo = mid + 1;
-                    else hi = mid;
-                }
-                rank += lo;
-            }
-            if (rank < k) sorted[rank] = key;
-        }
-        if (mine) atomicAdd(&sc.count, (uint32_t) mine);
+        return nk;
+    }
+    // the long way: squeeze out the empty slots (the order does not matter to the selection), then select
+    __syncthreads();
+    if (tid == 0) sc.count = 0u;
+    __syncthreads();
+    for (int base = 0; base < total; base += NT) {
+        const int i = base + tid;
+        const uint64_t key = i < total ? buf[i] : 0ull;
         __syncthreads();
-        nk = (int) min(sc.count, (uint32_t) k);
-    } else {
-        if (tid == 0) sc.count = 0u;
-        __syncthreads();
-        // squeeze out the empty slots (the order does not matter to the selection)
-        for (int base = 0; base < total; base += NT) {
-            const int i = base + tid;
-            const uint64_t key = i < total ? buf[i] : 0ull;
-            __syncthreads();
-            if (key != 0ull) buf[atomicAdd(&sc.count, 1u)] = key;
-            __syncthreads();
-        }
-        const int n = (int) sc.count;
-        __syncthreads();
-        const uint64_t tau = block_kth_key<NT>(buf, n, k, sc);
-        nk = block_take<NT>(buf, n, k, tau, sel, sc);
-        for (int j = nk + tid; j < k_cap; j += NT) sorted[j] = 0ull;
-        block_rank_sort<NT>(sel, nk, sorted);
+        if (key != 0ull) buf[atomicAdd(&sc.count, 1u)] = key;
         __syncthreads();
     }
+    const int m = (int) sc.count;
+    __syncthreads();
+    const uint64_t tau = block_kth_key<NT>(buf, m, k, sc);
+    nk = block_take<NT>(buf, m, k, tau, sel, sc);
+    block_rank_sort<NT>(sel, nk, sorted);
+    __syncthreads();
     return nk;
 }
 
@@ -240,24 +257,49 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         if (tid == 0) *out_token = key_id(sorted[0]);
         return;
     }
+    // The two exponentials of a candidate go to different halves of the block, so they run side by side.
     const double v0 = (double) key_value(sorted[0]);
-    for (int j = tid; j < nk; j += NT) {
-        const double d = (double) key_value(sorted[j]) - v0;
-        pj[j] = exp(d);
-        acc[j] = exp(d / p.temperature);
+    {
+        const bool second = tid >= NT / 2;
+        for (int j = second ? tid - NT / 2 : tid; j < nk; j += NT / 2) {
+            const double d = (double) key_value(sorted[j]) - v0;
+            if (second) acc[j] = exp(d / p.temperature);
+            else pj[j] = exp(d);
+        }
     }
     __syncthreads();
     volatile double * sum_slot = reinterpret_cast<volatile double *>(&sc.hist[0]);
-    if (tid == 0) {
+    if (tid == 0) {  // left to right, as the reference adds; eight loads ahead of the additions
         double sum = 0.0;
-        for (int j = 0; j < nk; ++j) sum += pj[j];
+        int j = 0;
+        for (; j + 8 <= nk; j += 8) {
+            double t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = pj[j + u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) sum += t[u];
+        }
+        for (; j < nk; ++j) sum += pj[j];
         *sum_slot = sum;
     } else if (tid == 32) {
         double run = 0.0;
-        for (int j = 0; j < nk; ++j) {
+        int j = 0;
+        for (; j + 8 <= nk; j += 8) {
+            double t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = acc[j + u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                run += t[u];
+                acc[j + u] = run;
+            }
+        }
+        for (; j < nk; ++j) {
             run += acc[j];
             acc[j] = run;
         }
+    } else if (tid == 64) {  // the uniform does not depend on the sums
+        reinterpret_cast<volatile double *>(&sc.hist[0])[1] = philox_uniform(p.seed, p.counter);
     }
     __syncthreads();
     {
@@ -268,9 +310,20 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
     if (tid == 0) {
         int keep = nk;
         double cum = 0.0;
-        for (int j = 0; j < nk; ++j) {
-            cum += qj[j];
-            if (cum >= p.top_p) { keep = j + 1; break; }
+        bool cut = false;
+        for (int j0 = 0; j0 < nk && !cut; j0 += 8) {
+            double t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = j0 + u < nk ? qj[j0 + u] : 0.0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (cut || j0 + u >= nk) continue;
+                cum += t[u];
+                if (cum >= p.top_p) {
+                    keep = j0 + u + 1;
+                    cut = true;
+                }
+            }
         }
         if (p.min_p > 0.0f) {
             int m = 1;
@@ -278,7 +331,7 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
             keep = m;
         }
         const double wsum = acc[keep - 1];
-        const double u = philox_uniform(p.seed, p.counter) * wsum;
+        const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
         int pick = keep - 1;
         for (int j = 0; j < keep; ++j)
             if (u < acc[j]) { pick = j; break; }
@@ -385,7 +438,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     uint32_t * tcnt = tkey + TS;                                // [TS]
     uint32_t * taint = tcnt + TS;                               // [NT] per thread: its largest history logit
     uint32_t * notplain = taint + NT;                           // [32] per epoch: warps that must look at the bit set
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(notplain + 32);
+    uint32_t * notempty = notplain + 32;                        // [32] per epoch: warps that have an allowed element
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(notempty + 32);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
@@ -434,7 +488,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         tcnt[i] = 0u;
     }
     taint[tid] = 0u;
-    if (tid < 32) notplain[tid] = 0u;
+    if (tid < 32) notplain[tid] = notempty[tid] = 0u;
     if (tid < 16) {  // addend per mask nibble: 0 keeps an element, -inf removes it from every maximum
         lut[tid] = make_float4((tid & 1) ? 0.0f : -INFINITY, (tid & 2) ? 0.0f : -INFINITY, (tid & 4) ? 0.0f : -INFINITY,
                                (tid & 8) ? 0.0f : -INFINITY);
@@ -452,9 +506,12 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             if (m[u]) epm |= 1u << (w / (kEpoch / 32));
             // A warp whose words of an epoch are all ones streams that epoch without looking at the bit set.  Word r
             // of a vector row belongs to the threads r * 32 / VEC ..., that is to warp r / VEC.
-            const uint32_t reader = m[u] != 0xffffffffu ? 1u << ((w % kWordsPerVec) / VEC) : 0u;
-            const uint32_t readers = __reduce_or_sync(kFull, reader);
-            if (lane == 0 && readers) atomicOr(&notplain[w / (kEpoch / 32)], readers);
+            // A warp whose words of an epoch are all zeros skips the epoch.
+            const uint32_t reader = 1u << ((w % kWordsPerVec) / VEC);
+            const uint32_t holed = __reduce_or_sync(kFull, m[u] != 0xffffffffu ? reader : 0u);
+            const uint32_t alive = __reduce_or_sync(kFull, m[u] != 0u ? reader : 0u);
+            if (lane == 0 && holed) atomicOr(&notplain[w / (kEpoch / 32)], holed);
+            if (lane == 0 && alive) atomicOr(&notempty[w / (kEpoch / 32)], alive);
         }
         cnt = __reduce_add_sync(kFull, cnt);
         epm = __reduce_or_sync(kFull, epm);
@@ -572,8 +629,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     // slice has at least k elements >= v, so nothing below v can be among its best k.  A warp splits into r
     // groups of lanes (r a power of two), takes each group's maximum and publishes the smallest of them: r
     // different lanes have reached it.  The bound is the minimum over the warps (for k = 1: the maximum).  It is
-    // made after the first epoch, refreshed after the fourth, and tightened at the end (flags are cheap: only the
-    // few threads that hold a candidate ever look at theirs).
+    // made after the first epoch, refreshed after the second and the fourth, and tightened at the end (flags are
+    // cheap: only the few threads that hold a candidate ever look at theirs; under a mask that leaves some lanes
+    // without an element for long there is simply no running bound, and everything is flagged).
     const uint32_t * effp = eff + ((tid * VEC) >> 5);
     const int bshift = (tid * VEC) & 31;
     const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
@@ -586,10 +644,13 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     int done = 0;
 
     uint32_t taint_w = 0u;  // this thread's taint, read when the first bound is made
+    int next_refresh = 0;   // the bound is refreshed after this many epochs (the same in all lanes of a warp)
     auto clean_max = [&]() -> float { return (tmax > -INFINITY && order_word(tmax) > taint_w) ? tmax : -INFINITY; };
     auto issue = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
-        const bool plain = !((notplain[ep] >> warp) & 1u);  // the same for the whole warp
-        if (plain) {
+        // the same for the whole warp: 0 = nothing allowed here, 1 = everything allowed, 2 = mixed
+        const int cls = !((notempty[ep] >> warp) & 1u) ? 0 : (!((notplain[ep] >> warp) & 1u) ? 1 : 2);
+        if (cls == 0) return cls;
+        if (cls == 1) {
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 mb[i] = kVecBits;
@@ -602,11 +663,13 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
             }
         }
-        return plain;
+        return cls;
     };
-    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
+    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], int cls) {
         float vmx[NV], emax = -INFINITY;
-        if (plain) {  // every element counts (history ids too: see taint)
+#pragma unroll
+        for (int i = 0; i < NV; ++i) vmx[i] = -INFINITY;
+        if (cls == 1) {  // every element counts (history ids too: see taint)
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 float m = xv[i][0];
@@ -615,7 +678,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 vmx[i] = m;
                 emax = fmaxf(emax, m);
             }
-        } else {
+        } else if (cls == 2) {
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 float m = -INFINITY;
@@ -647,7 +710,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
 #ifdef FNS_X_NOREFRESH
         if (bounded && done == 0)
 #else
-        if (__builtin_expect(bounded && (done == 0 || done == 3), 0))
+        if (__builtin_expect(bounded && done == next_refresh, 0))
 #endif
         {
             if (done == 0 && n_own > 0) {  // uniform: the owners have published their taint before their first reduce
@@ -655,6 +718,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 taint_w = taint[tid];
             }
             thr_v = block_bound<NT>(clean_max(), thr_v, lanes_per_group, done == 0, k == 1, sh);
+            next_refresh = done == 0 ? 1 : (done == 1 ? 3 : -1);  // after epochs 1, 2 and 4, then not before the end
         }
         ++done;
         if (__builtin_expect(emax >= thr_v, 0)) {
@@ -669,6 +733,39 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             if (ep < EPW) f0 |= hb << (ep * FPE);
             else f1 |= hb << ((ep - EPW) * FPE);
         }
+    };
+    // The final bound (every thread of the block calls it at the same point).  After the lane-group bound it is
+    // tightened to (nearly) the k-th largest of the threads' maxima: k threads that have reached a value are k
+    // elements that have, and a count over the block is one barrier.  The search runs bit by bit below the highest
+    // bit in which the bound so far and the block's maximum differ.
+    auto tighten = [&](float cmax) {
+        copy_word_wait();  // this thread's logit copies have landed; the barriers below show them to the others
+        const uint32_t wt = cmax > -INFINITY ? order_word(cmax) : 0u;  // this thread's witness as an order word
+        if (bounded && done > 0) {
+            const uint32_t top = __reduce_max_sync(kFull, wt);
+            if (lane == 0) sh.warp_top[warp] = top;
+            thr_v = block_bound<NT>(cmax, thr_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
+            if (k > 1 && k <= NT) {
+                uint32_t hi_w = sh.warp_top[0];
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) hi_w = max(hi_w, sh.warp_top[w]);
+                const uint32_t lo_w = order_word(thr_v);
+                if (hi_w > lo_w) {
+                    const int split = 31 - __clz((int) (lo_w ^ hi_w));
+                    uint32_t bw = split == 31 ? 0u : (lo_w & ~((2u << split) - 1u));  // the common prefix: <= lo_w, so valid
+                    const int stop = split > 10 ? split - 10 : 0;
+#pragma unroll 1
+                    for (int bit = split; bit >= stop; --bit) {
+                        const uint32_t cand = bw | (1u << bit);
+                        if (__syncthreads_count(wt >= cand) >= k) bw = cand;
+                    }
+                    if (bw > lo_w) thr_v = word_value(bw);
+                }
+            }
+        } else {
+            __syncthreads();
+        }
+        thr_v += 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
     };
     constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
     const uint32_t epochs = todo;          // (the loop below consumes `todo`)
@@ -705,8 +802,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             vmx[u] = mb[u] ? vector_max<VEC>(xv[u], mb[u]) : -INFINITY;
             tmax = fmaxf(tmax, vmx[u]);
         }
-        if (bounded) thr_v = block_bound<NT>(tmax, thr_v, lanes_per_group, true, k == 1, sh);
         done = 1;
+        tighten(tmax);
         const uint64_t tk0 = (uint64_t) order_word(thr_v) << 32;
 #pragma unroll
         for (int u = 0; u < LPT; ++u) {
@@ -753,7 +850,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
         uint32_t ma[NV], mb[NV];
         int ea = next(), eb = -1;
-        bool pa = false, pb = false;
+        int pa = 0, pb = 0;
         if (ea >= 0) pa = issue(ea, xa, ma);
         bool first = true;
         while (ea >= 0) {
@@ -775,37 +872,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             reduce(eb, xb, mb, pb);
         }
     }
-    copy_word_wait();  // this thread's logit copies have landed; the barrier below shows them to the others
-    const float cmax = clean_max();
-    const uint32_t wt = cmax > -INFINITY ? order_word(cmax) : 0u;  // this thread's witness as an order word
-    if (bounded && done > 0) {
-        const uint32_t top = __reduce_max_sync(kFull, wt);
-        if (lane == 0) sh.warp_top[warp] = top;
-        thr_v = block_bound<NT>(cmax, thr_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
-        // The bound is now tightened to (nearly) the k-th largest of the threads' maxima: k threads that have
-        // reached a value are k elements that have, and a count over the block is one barrier.  The search runs
-        // bit by bit below the highest bit in which the bound so far and the block's maximum differ.
-        if (k > 1 && k <= NT) {
-            uint32_t hi_w = sh.warp_top[0];
-#pragma unroll
-            for (int w = 1; w < kWarps; ++w) hi_w = max(hi_w, sh.warp_top[w]);
-            const uint32_t lo_w = order_word(thr_v);
-            if (hi_w > lo_w) {
-                const int split = 31 - __clz((int) (lo_w ^ hi_w));
-                uint32_t bw = split == 31 ? 0u : (lo_w & ~((2u << split) - 1u));  // the common prefix: <= lo_w, so valid
-                const int stop = split > 13 ? split - 13 : 0;
-#pragma unroll 1
-                for (int bit = split; bit >= stop; --bit) {
-                    const uint32_t cand = bw | (1u << bit);
-                    if (__syncthreads_count(wt >= cand) >= k) bw = cand;
-                }
-                if (bw > lo_w) thr_v = word_value(bw);
-            }
-        }
-    } else {
-        __syncthreads();
-    }
-    thr_v += 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
+    FNS_PHASE(9)
+    if (!sparse) tighten(clean_max());
     if (!(tmax >= thr_v)) f0 = f1 = 0ull;  // nothing of this thread can be a candidate: its flags are void
     FNS_PHASE(2)
 
@@ -908,22 +976,39 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 }
             }
         }
+        FNS_PHASE(6)
         // (c) The flagged groups.  Their vectors go on a work list that the whole block then shares: one vector per
         // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
         // careful way walks every epoch instead, one per round, with a vote after each.
         bool listed = true;
         if (!careful) {
+            // one reservation per warp: a prefix sum over the lanes' flag counts
+            const int mine_n = (__popcll(f0) + __popcll(f1)) * VPF;
+            int upto = mine_n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kFull, upto, o);
+                if (lane >= o) upto += t;
+            }
+            const int warp_n = __shfl_sync(kFull, upto, 31);
+            uint32_t at = 0u;
+            if (lane == 31 && warp_n) at = atomicAdd(&sh.n_vl, (uint32_t) warp_n);
+            at = __shfl_sync(kFull, at, 31) + (uint32_t) (upto - mine_n);
             while ((f0 | f1) != 0ull) {
                 const int b = pop_flag();
                 const int ep = b / FPE, g = b - ep * FPE;
 #pragma unroll
                 for (int u = 0; u < VPF; ++u) {
-                    const uint32_t at = atomicAdd(&sh.n_vl, 1u);
                     if (at < (uint32_t) a.list_cap) vlist[at] = (uint32_t) (ep * NT * NV + (g * VPF + u) * NT + tid);
+                    ++at;
                 }
             }
             __syncthreads();
+            FNS_PHASE(7)
             const int n_work = (int) sh.n_vl;
+#ifdef FNS_PHASE_TIMING
+            if (tid == 0 && blockIdx.x == 0 && blockIdx.y < 1024) { g_rowphase[blockIdx.y][12] = (unsigned) n_work; g_rowphase[blockIdx.y][13] = (unsigned) n_own; g_rowphase[blockIdx.y][14] = sh.n_cand; }
+#endif
             listed = n_work <= a.list_cap;  // uniform; a list that does not fit sends the slice the careful way
 #pragma unroll 1
             for (int i = tid; i < n_work && listed; i += NT) {
@@ -1018,6 +1103,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         }
     } else {
         const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
+#ifdef FNS_PHASE_TIMING
+        if (tid == 0 && blockIdx.x == 0 && blockIdx.y < 1024) g_rowphase[blockIdx.y][11] = (unsigned) n;
+#endif
         uint64_t * dst = whole_row ? sorted : out;
         int got;
         if (n <= kRankSelectMax) {
@@ -1082,7 +1170,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     }
     __syncthreads();
     FNS_PHASE(7)
-    const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, sh.sc, k, a.k_cap);
+    const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, reinterpret_cast<uint64_t *>(pj), 2 * a.k_cap, sh.sc, k, a.k_cap);
     FNS_PHASE(9)
     draw_tail<NT>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
     FNS_PHASE(5)
@@ -1129,7 +1217,8 @@ __global__ void __launch_bounds__(kFinalThreads) k_finalize(const FinalArgs a) {
         buf[i] = cand_to_key(a.cands[row_base + (size_t) l * a.list_stride + j]);
     }
     __syncthreads();
-    const int nk = merge_lists<kFinalThreads>(buf, a.lists, a.list_len, sel, sorted, sh.sc, k, a.k_cap);
+    const int nk = merge_lists<kFinalThreads>(buf, a.lists, a.list_len, sel, sorted, reinterpret_cast<uint64_t *>(pj),
+                                              2 * a.k_cap, sh.sc, k, a.k_cap);
     draw_tail<kFinalThreads>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap,
                              a.out_tokens ? a.out_tokens + row : nullptr,
                              a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
@@ -1250,7 +1339,7 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     if (hist_bound > 0) pl.own_cap = round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4);
     pl.list_cap = pl.threads * 8;  // the sparse path lists at most 8 vectors per thread
     pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.own_cap * 8 +
-                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + 128 + sizeof(SelectShared) + 16;
+                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + 256 + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
 
@@ -1598,10 +1687,15 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
 
 #ifdef FNS_PHASE_TIMING
 // development aid (not part of the ABI header): reads and clears the phase clocks
+int fns_b200_debug_rowphases(unsigned * out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, fnsb::g_rowphase, sizeof(unsigned) * 1024 * 16);
+    return 0;
+}
 int fns_b200_debug_phases(unsigned long long * out8) {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 16);
-    unsigned long long zero[16] = {};
+    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 32);
+    unsigned long long zero[32] = {};
     cudaMemcpyToSymbol(fnsb::g_phase, zero, sizeof zero);
     return 0;
 }

@@ -466,6 +466,49 @@ def test_adversarial_orders_force_repeated_compaction(dev, oracle):
         check_against_oracle(oracle, w, tokens, cands)
 
 
+def test_history_of_the_largest_logits_with_repeats_and_every_penalty_sign(dev, oracle):
+    """The history holds exactly the ids a sampler would pick: the largest logits of the row, many of them several
+    times.  Unmasked rows stream these ids at their raw value (they must not count as witnesses for the bound);
+    the occurrence counts decide which of them stay candidates; a negative frequency penalty raises a value with
+    every occurrence; a history longer than one round of the scatter takes the slow publishing path."""
+    g = wl.rng(123)
+    rows, n = 6, 151_936
+    x = wl.gaussian_logits(g, rows, n, 2.5)
+    top = np.argsort(-x, axis=1)[:, :400].astype(np.int32)
+    hist = np.zeros((rows, 6000), np.int32)
+    hlen = np.zeros(rows, np.int32)
+    for r in range(rows):
+        reps = g.integers(1, 9, size=400)
+        ids = np.repeat(top[r], reps)
+        g.shuffle(ids)
+        ids = ids[: min(ids.size, 6000 if r % 2 else 1500)]
+        hist[r, : ids.size] = ids
+        hlen[r] = ids.size
+    p = make_params(rows, temperature=0.8, top_k=64, top_p=0.97, repetition=1.15, presence=0.6, frequency=0.25)
+    p["frequency"][2] = -0.2   # more occurrences raise the value
+    p["presence"][3] = -1.5    # penalised above raw
+    p["repetition"][4] = 0.8
+    p["frequency"][5] = 0.0    # no counts needed
+    p["top_k"][1] = 7
+    p["seed"] = np.arange(rows, dtype=np.uint64) + 5
+    w = wl.Workload("hot_history", x, p, None, hist, hlen)
+    for slices in (0, 1, 5):
+        tokens, cands = run_rows(w, dev, slices=slices, max_history=6000)
+        check_against_oracle(oracle, w, tokens, cands)
+    # the same under a mask that cuts the row into allowed and excluded runs
+    w.masks = np.stack([wl.run_mask(g, n, 0.6, 20) for _ in range(rows)])
+    tokens, cands = run_rows(w, dev, max_history=6000)
+    check_against_oracle(oracle, w, tokens, cands)
+
+
+def test_whole_row_blocks_at_batch_sizes_around_the_sm_count(dev, oracle):
+    """At 148 rows and more a row is one 512-thread block; just below, rows are cut into slices."""
+    for rows in (147, 149, 300):
+        w = wl.session_batch(seed=40 + rows, rows=rows, vocab=50_000, history=300)
+        tokens, cands = run_rows(w, dev)
+        check_against_oracle(oracle, w, tokens, cands)
+
+
 # ---- vocabulary shards on one GPU (the exchange itself is tested with gloo on CPU and nccl on >1 GPU) -------
 @pytest.mark.parametrize("shards", [2, 4, 8])
 def test_vocab_shards_merge_to_the_unsharded_answer(dev, oracle, shards):
