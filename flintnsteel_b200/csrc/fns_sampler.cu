@@ -85,6 +85,7 @@ struct SelectArgs {
     int trigger;     // compact when the buffer holds this many
     int own_cap;     // entries of the list of owned history ids (a multiple of 4), 0: no penalties
     int list_cap;    // entries of the allowed-vector list of a sparse slice
+    int seg_cap;     // segments of a slice (32 vectors each), a multiple of 4
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
     int32_t * out_tokens;       // [rows], may be null
@@ -98,12 +99,12 @@ struct SelectShared {
     uint32_t n_cand;      // append cursor; may run past cap (the excess was not stored: see `lost`)
     uint32_t n_own;       // history ids of the slice that the mask allows, each once
     uint32_t n_vl;        // cursor of the allowed-vector list
+    uint32_t n_seg;       // segments with an allowed element
     int keep;
     int is_last;
     __align__(16) float warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
     uint32_t warp_top[kMaxWarps];               // per warp: its largest thread maximum (as an order word)
     uint32_t red_cnt[kMaxWarps];                // per warp: vectors with an allowed element
-    uint32_t red_ep[kMaxWarps];                 // per warp: epochs with an allowed element
     uint64_t red[kMaxWarps];
 };
 
@@ -412,7 +413,6 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     constexpr int kWarps = NT / 32;
     constexpr uint32_t kVecBits = VEC == 32 ? 0xffffffffu : (1u << VEC) - 1u;
     constexpr int kWordsPerVec = NT * VEC / 32;              // bit-set words between two vectors of one thread
-    constexpr int MW = 16;                                   // mask words per thread requested together
     static_assert(32 * FPE <= 128, "two 64-bit flag words hold the longest slice");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -430,16 +430,16 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     double * pj = reinterpret_cast<double *>(sorted + a.k_cap);
     double * acc = pj + a.k_cap;
     uint32_t * eff = reinterpret_cast<uint32_t *>(acc + a.k_cap);
-    uint32_t * own = eff + a.slice_len / 32;
+    uint32_t * own = eff + a.slice_len / 32 + 8;  // (8 zero words follow the bit set: the bits of the list's padding)
     uint32_t * oval = own + a.own_cap;
     float4 * lut = reinterpret_cast<float4 *>(oval + a.own_cap);
     uint32_t * vlist = reinterpret_cast<uint32_t *>(lut + 16);  // [list_cap] allowed vectors of a sparse slice
     uint32_t * tkey = vlist + a.list_cap;                       // [TS] in-slice offsets whose occurrences are counted
     uint32_t * tcnt = tkey + TS;                                // [TS]
     uint32_t * taint = tcnt + TS;                               // [NT] per thread: its largest history logit
-    uint32_t * notplain = taint + NT;                           // [32] per epoch: warps that must look at the bit set
-    uint32_t * notempty = notplain + 32;                        // [32] per epoch: warps that have an allowed element
-    SelectShared & sh = *reinterpret_cast<SelectShared *>(notempty + 32);
+    uint16_t * seglist = reinterpret_cast<uint16_t *>(taint + NT);  // [seg_cap] segments with an allowed element
+    uint16_t * segpos = seglist + a.seg_cap;                    // [seg_cap] segment -> its place in the list
+    SelectShared & sh = *reinterpret_cast<SelectShared *>(segpos + a.seg_cap);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
@@ -471,54 +471,95 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
     };
     const int words = (n_s + 31) >> 5;
-    uint32_t m[MW];  // this thread's words of the mask: slice_len / 32 <= NT * MW
-#pragma unroll
-    for (int u = 0; u < MW; ++u) {  // independent loads, all in flight together
-        const int w = u * NT + tid;
-        m[u] = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
-    }
     if (tid == 0) {
         sh.n_cand = 0u;
         sh.thr_key = 0ull;
         sh.n_own = 0u;
         sh.n_vl = 0u;
+        sh.n_seg = 0u;
     }
     for (int i = tid; i < TS; i += NT) {
         tkey[i] = kNoKey;
         tcnt[i] = 0u;
     }
     taint[tid] = 0u;
-    if (tid < 32) notplain[tid] = notempty[tid] = 0u;
+    if (tid < 8) eff[a.slice_len / 32 + tid] = 0u;
     if (tid < 16) {  // addend per mask nibble: 0 keeps an element, -inf removes it from every maximum
         lut[tid] = make_float4((tid & 1) ? 0.0f : -INFINITY, (tid & 2) ? 0.0f : -INFINITY, (tid & 4) ? 0.0f : -INFINITY,
                                (tid & 8) ? 0.0f : -INFINITY);
     }
     __syncthreads();
     {
-        uint32_t cnt = 0u, epm = 0u;
+        // The bit set, the number of allowed elements, and the list of SEGMENTS that have one.  A segment is what
+        // one warp loads with one instruction: 32 consecutive vectors, WPS mask words; here every thread takes
+        // whole segments (one 16-byte load of mask words where the row of masks allows it).  Pass 1 walks the
+        // list, so excluded stretches of the row cost nothing and every warp gets the same share; an entry also
+        // says whether the whole segment is allowed (then nobody looks at the bit set again).
+        constexpr int WPS = VEC;  // mask words per segment
+        constexpr int SU = 4;     // segments per thread requested together
+        const int slice_segs = a.slice_len / (32 * VEC);
+        const uint32_t below = (1u << lane) - 1u;
+        const uint32_t tail = (n_s & 31) ? (1u << (n_s & 31)) - 1u : 0xffffffffu;
+        const bool wide = WPS >= 4 && mrow && (reinterpret_cast<uintptr_t>(mrow) & 15u) == 0;
+        uint32_t cnt = 0u;
+#pragma unroll 1
+        for (int s0 = 0; s0 < slice_segs; s0 += NT * SU) {  // one round for slices up to 2048 * NT / 512 segments
+            uint32_t mw[SU][WPS];
 #pragma unroll
-        for (int u = 0; u < MW; ++u) {
-            const int w = u * NT + tid;
-            if (w >= a.slice_len / 32) continue;  // uniform per warp: 32 divides slice_len / 32
-            if (w == words - 1 && (n_s & 31)) m[u] &= (1u << (n_s & 31)) - 1u;
-            eff[w] = m[u];
-            cnt += (uint32_t) __popc(vector_units(m[u]));
-            if (m[u]) epm |= 1u << (w / (kEpoch / 32));
-            // A warp whose words of an epoch are all ones streams that epoch without looking at the bit set.  Word r
-            // of a vector row belongs to the threads r * 32 / VEC ..., that is to warp r / VEC.
-            // A warp whose words of an epoch are all zeros skips the epoch.
-            const uint32_t reader = 1u << ((w % kWordsPerVec) / VEC);
-            const uint32_t holed = __reduce_or_sync(kFull, m[u] != 0xffffffffu ? reader : 0u);
-            const uint32_t alive = __reduce_or_sync(kFull, m[u] != 0u ? reader : 0u);
-            if (lane == 0 && holed) atomicOr(&notplain[w / (kEpoch / 32)], holed);
-            if (lane == 0 && alive) atomicOr(&notempty[w / (kEpoch / 32)], alive);
+            for (int u = 0; u < SU; ++u) {  // independent loads, all in flight together
+                const int w0 = (s0 + u * NT + tid) * WPS;
+                if constexpr (WPS >= 4) {
+                    if (wide && w0 + WPS <= words) {
+#pragma unroll
+                        for (int q = 0; q < WPS; q += 4) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(mrow + w0 + q);
+                            mw[u][q] = v.x;
+                            mw[u][q + 1] = v.y;
+                            mw[u][q + 2] = v.z;
+                            mw[u][q + 3] = v.w;
+                        }
+                        continue;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < WPS; ++q) mw[u][q] = w0 + q < words ? (mrow ? mrow[w0 + q] : 0xffffffffu) : 0u;
+            }
+            uint32_t lead[SU], whole[SU];
+            int n_mine = 0;
+#pragma unroll
+            for (int u = 0; u < SU; ++u) {
+                const int seg = s0 + u * NT + tid;
+                uint32_t any = 0u, all = 0xffffffffu;
+                if (seg < slice_segs) {
+#pragma unroll
+                    for (int q = 0; q < WPS; ++q) {
+                        if (seg * WPS + q == words - 1) mw[u][q] &= tail;
+                        any |= mw[u][q];
+                        all &= mw[u][q];
+                        cnt += (uint32_t) __popc(mw[u][q]);
+                        eff[seg * WPS + q] = mw[u][q];
+                    }
+                }
+                lead[u] = __ballot_sync(kFull, any != 0u);
+                whole[u] = __ballot_sync(kFull, any != 0u && all == 0xffffffffu);
+                n_mine += __popc(lead[u]);
+            }
+            uint32_t at = 0u;
+            if (lane == 0 && n_mine) at = atomicAdd(&sh.n_seg, (uint32_t) n_mine);
+            at = __shfl_sync(kFull, at, 0);
+#pragma unroll
+            for (int u = 0; u < SU; ++u) {
+                if ((lead[u] >> lane) & 1u) {
+                    const uint32_t seg = (uint32_t) (s0 + u * NT + tid);
+                    const uint32_t pos = at + (uint32_t) __popc(lead[u] & below);
+                    seglist[pos] = (uint16_t) (seg | (((whole[u] >> lane) & 1u) << 15));
+                    segpos[seg] = (uint16_t) pos;
+                }
+                at += (uint32_t) __popc(lead[u]);
+            }
         }
         cnt = __reduce_add_sync(kFull, cnt);
-        epm = __reduce_or_sync(kFull, epm);
-        if (lane == 0) {
-            sh.red_cnt[warp] = cnt;
-            sh.red_ep[warp] = epm;
-        }
+        if (lane == 0) sh.red_cnt[warp] = cnt;
     }
     const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
     const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
@@ -529,13 +570,14 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     uint32_t lost = 0u;        // elements of the current round that found the buffer full
     __syncthreads();
     FNS_PHASE(0)
-    int n_av = 0;              // vectors with an allowed element, before the history is taken out
-    uint32_t todo = 0u;        // epochs with an allowed element
+    int n_av = 0;              // allowed elements (so at most that many vectors with one), before the history is taken out
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        n_av += (int) sh.red_cnt[w];
-        todo |= sh.red_ep[w];
-    }
+    for (int w = 0; w < kWarps; ++w) n_av += (int) sh.red_cnt[w];
+    const int n_seg = (int) sh.n_seg;
+    const int n_groups = (n_seg + kWarps * NV - 1) / (kWarps * NV);  // a group: NV consecutive list entries per warp
+    // the last group is filled up with a segment behind the slice, whose bits (the zero words after the bit set)
+    // exclude everything: no loop below has to ask where the list ends
+    for (int i = n_seg + tid; i < n_groups * kWarps * NV; i += NT) seglist[i] = (uint16_t) (a.slice_len / (32 * VEC));
 
     // 2. Penalties.  Every history id (plus the draft prefix of a verification column) that lies in the slice
     // clears its bit in the bit set, so the streaming pass never sees it and pays nothing for penalties.  The
@@ -553,7 +595,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     auto publish_taint = [&](uint32_t slot) {
         const uint32_t off = own[slot];
         const float raw = value_in_word(oval[slot], x + off);
-        if (is_finite(raw)) atomicMax(&taint[(off / VEC) & (NT - 1)], order_word(raw));
+        const uint32_t vec = off / VEC;  // streamed by lane vec % 32 of the warp that the segment's list place gives
+        if (is_finite(raw)) atomicMax(&taint[((segpos[vec >> 5] / NV) % kWarps) * 32 + (vec & 31u)], order_word(raw));
     };
     if (use_hist && n_pen > 0) {
         const uint32_t below = (1u << lane) - 1u;
@@ -620,56 +663,78 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     }
     FNS_PHASE(1)
 
-    // 3. Pass 1 over the slice: maxima only.  An epoch gives every thread NV vectors (16 elements); two epochs
-    // are in flight (the loads of the next one are issued before the current one is reduced); a vector whose
-    // elements the bit set excludes is not loaded.  Excluded elements of a loaded vector get -inf added (a table
-    // lookup by the vector's mask nibble), so the maxima need no branches.  Every thread keeps the maximum of
-    // what it has seen; a vector group whose maximum reaches the running bound sets a flag bit and is read again
-    // in pass 2.  The bound needs no buffer: if r lanes of EVERY warp hold a maximum >= v (r * warps >= k), the
-    // slice has at least k elements >= v, so nothing below v can be among its best k.  A warp splits into r
+    // 3. Pass 1 over the listed segments: maxima only.  A group gives every warp NV segments, that is every thread
+    // NV vectors (16 elements); two groups are in flight (the loads of the next one are issued before the current
+    // one is reduced).  In a segment that is allowed as a whole nobody looks at the bit set; elsewhere a vector
+    // whose elements the bit set excludes is not loaded, and excluded elements of a loaded vector get -inf added (a
+    // table lookup by the vector's mask nibble), so the maxima need no branches.  Every thread keeps the maximum
+    // of what it has seen; a vector group whose maximum reaches the running bound sets a flag bit and is read
+    // again in pass 2.  The bound needs no buffer: if r lanes of EVERY warp hold a maximum >= v (r * warps >= k),
+    // the slice has at least k elements >= v, so nothing below v can be among its best k.  A warp splits into r
     // groups of lanes (r a power of two), takes each group's maximum and publishes the smallest of them: r
     // different lanes have reached it.  The bound is the minimum over the warps (for k = 1: the maximum).  It is
-    // made after the first epoch, refreshed after the second and the fourth, and tightened at the end (flags are
+    // made after the first group, refreshed after the second and the fourth, and tightened at the end (flags are
     // cheap: only the few threads that hold a candidate ever look at theirs; under a mask that leaves some lanes
     // without an element for long there is simply no running bound, and everything is flagged).
-    const uint32_t * effp = eff + ((tid * VEC) >> 5);
-    const int bshift = (tid * VEC) & 31;
     const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above the bound
     const bool bounded = r_need <= 32;             // otherwise every group is flagged
     int lanes_per_group = 32;                      // 32 / (r_need rounded up to a power of two)
     while (lanes_per_group > 1 && (32 / lanes_per_group) < r_need) lanes_per_group >>= 1;
     float tmax = -INFINITY;                        // this thread's maximum so far
     float thr_v = -FLT_MAX;                        // the bound: x < thr_v cannot be a candidate
-    uint64_t f0 = 0ull, f1 = 0ull;                 // flag bit ep * FPE + g: group g of epoch ep reached the bound
+    uint64_t f0 = 0ull, f1 = 0ull;                 // flag bit g * FPE + j: vector group j of list group g reached the bound
     int done = 0;
-
     uint32_t taint_w = 0u;  // this thread's taint, read when the first bound is made
-    int next_refresh = 0;   // the bound is refreshed after this many epochs (the same in all lanes of a warp)
+    int next_refresh = 0;   // the bound is refreshed after this many groups (the same in all lanes of a warp)
     auto clean_max = [&]() -> float { return (tmax > -INFINITY && order_word(tmax) > taint_w) ? tmax : -INFINITY; };
-    auto issue = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) {
-        // the same for the whole warp: 0 = nothing allowed here, 1 = everything allowed, 2 = mixed
-        const int cls = !((notempty[ep] >> warp) & 1u) ? 0 : (!((notplain[ep] >> warp) & 1u) ? 1 : 2);
-        if (cls == 0) return cls;
-        if (cls == 1) {
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                mb[i] = kVecBits;
-                load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
-            }
+    // This warp's NV list entries of group g (consecutive places: consecutive segments, one read).
+    const uint16_t * my_entries = seglist + warp * NV;
+    auto entries_of = [&](int g, uint32_t (&en)[NV]) {
+        const uint16_t * at = my_entries + g * (kWarps * NV);
+        if constexpr (NV == 4) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(at);
+            en[0] = v.x & 0xffffu;
+            en[1] = v.x >> 16;
+            en[2] = v.y & 0xffffu;
+            en[3] = v.y >> 16;
+        } else if constexpr (NV == 2) {
+            const uint32_t v = *reinterpret_cast<const uint32_t *>(at);
+            en[0] = v & 0xffffu;
+            en[1] = v >> 16;
         } else {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                mb[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-                if (mb[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
-            }
+            for (int i = 0; i < NV; ++i) en[i] = at[i];
         }
-        return cls;
     };
-    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], int cls) {
-        float vmx[NV], emax = -INFINITY;
+    const T * x_lane = x + lane * VEC;                           // this lane's vector of segment 0
+    const uint32_t * eff_lane = eff + ((lane * VEC) >> 5);       // the word with its bits, and where they start
+    const int eff_shift = (lane * VEC) & 31;
+    auto vector_bits = [&](uint32_t seg) -> uint32_t { return (eff_lane[seg * VEC] >> eff_shift) & kVecBits; };
+    auto vector_at = [&](uint32_t seg) -> const T * { return x_lane + seg * (32u * VEC); };
+    // Requests the NV vectors of group g.  Returns whether all of them lie in segments that are allowed as a whole
+    // (the same answer in every lane of the warp): then mb is not even written.
+    auto issue = [&](int g, float (&xv)[NV][VEC], uint32_t (&mb)[NV]) -> bool {
+        uint32_t en[NV];
+        entries_of(g, en);
+        uint32_t all = 0x8000u;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) vmx[i] = -INFINITY;
-        if (cls == 1) {  // every element counts (history ids too: see taint)
+        for (int i = 0; i < NV; ++i) all &= en[i];
+        if (all) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) load_vec<T, VEC>(vector_at(en[i] & 0x7fffu), xv[i]);
+            return true;
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t seg = en[i] & 0x7fffu;
+            mb[i] = (en[i] & 0x8000u) ? kVecBits : vector_bits(seg);
+            if (mb[i]) load_vec<T, VEC>(vector_at(seg), xv[i]);
+        }
+        return false;
+    };
+    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
+        float vmx[NV], emax = -INFINITY;
+        if (plain) {  // every element counts (history ids too: see taint)
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 float m = xv[i][0];
@@ -678,7 +743,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 vmx[i] = m;
                 emax = fmaxf(emax, m);
             }
-        } else if (cls == 2) {
+        } else {
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 float m = -INFINITY;
@@ -768,7 +833,6 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         thr_v += 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
     };
     constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
-    const uint32_t epochs = todo;          // (the loop below consumes `todo`)
     const bool sparse = n_av <= min(NT * LPT, a.list_cap);
     if (sparse) {
         // 3a. Few allowed vectors (a grammar mask that admits little): no epochs.  The allowed vectors are listed
@@ -817,7 +881,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 }
             }
         }
-        if (k > 1 && n_av * VEC + VEC > a.trigger) {  // uniform: only then can the buffer fill
+        if (k > 1 && n_av + VEC > a.trigger) {  // uniform: only then can the buffer fill
             uint64_t tk = tk0;
             while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
                 compact<NT>(buf, sel, k, a.cap, sh);
@@ -837,39 +901,27 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             }
         }
     } else {
-        auto next = [&]() -> int {
-            if (!todo) return -1;
-            const int ep = __ffs(todo) - 1;
-            todo &= todo - 1u;
-            return ep;
-        };
         float xa[NV][VEC], xb[NV][VEC];
 #pragma unroll
         for (int i = 0; i < NV; ++i)
 #pragma unroll
             for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
         uint32_t ma[NV], mb[NV];
-        int ea = next(), eb = -1;
-        int pa = 0, pb = 0;
-        if (ea >= 0) pa = issue(ea, xa, ma);
-        bool first = true;
-        while (ea >= 0) {
-            eb = next();
-            if (eb >= 0) pb = issue(eb, xb, mb);
-            if (first) {  // with two epochs requested: the history logits of this thread's ids, for the taint
-                first = false;
-                if (t_mine) {
-                    copy_word_wait();
+        bool pa = false, pb = false;
+        if (n_groups > 0) pa = issue(0, xa, ma);
+#pragma unroll 1
+        for (int g = 0; g < n_groups; g += 2) {
+            if (g + 1 < n_groups) pb = issue(g + 1, xb, mb);
+            if (g == 0 && t_mine) {  // with two groups requested: the history logits of this thread's ids, for the taint
+                copy_word_wait();
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if ((t_mine >> u) & 1u) publish_taint(t_base + ((t_pre >> (8 * u)) & 255u));
-                }
+                for (int u = 0; u < 4; ++u)
+                    if ((t_mine >> u) & 1u) publish_taint(t_base + ((t_pre >> (8 * u)) & 255u));
             }
-            reduce(ea, xa, ma, pa);
-            if (eb < 0) break;
-            ea = next();
-            if (ea >= 0) pa = issue(ea, xa, ma);
-            reduce(eb, xb, mb, pb);
+            reduce(g, xa, ma, pa);
+            if (g + 1 >= n_groups) break;
+            if (g + 2 < n_groups) pa = issue(g + 2, xa, ma);
+            reduce(g + 1, xb, mb, pb);
         }
     }
     FNS_PHASE(9)
@@ -999,7 +1051,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 const int ep = b / FPE, g = b - ep * FPE;
 #pragma unroll
                 for (int u = 0; u < VPF; ++u) {
-                    if (at < (uint32_t) a.list_cap) vlist[at] = (uint32_t) (ep * NT * NV + (g * VPF + u) * NT + tid);
+                    const uint32_t seg = my_entries[ep * (kWarps * NV) + g * VPF + u] & 0x7fffu;
+                    if (at < (uint32_t) a.list_cap) vlist[at] = (seg << 5) + (uint32_t) lane;
                     ++at;
                 }
             }
@@ -1027,14 +1080,19 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             }
         } else if (!sparse) {
 #pragma unroll 1
-            for (uint32_t m = epochs; m; m &= m - 1u) {
-                const int ep = __ffs(m) - 1;
+            for (int g = 0; g < n_groups; ++g) {
                 uint32_t bits[NV], lost = 0u;  // lost: elements of this round that found the buffer full
+                int e0[NV];                    // first element of each vector of this round
                 float xv[NV][VEC];
 #pragma unroll
+                uint32_t en[NV];
+                entries_of(g, en);
+#pragma unroll
                 for (int i = 0; i < NV; ++i) {
-                    bits[i] = (effp[ep * (kEpoch / 32) + i * kWordsPerVec] >> bshift) & kVecBits;
-                    if (bits[i]) load_vec<T, VEC>(x + (size_t) ((ep * NT * NV + i * NT + tid) * VEC), xv[i]);
+                    const uint32_t seg = en[i] & 0x7fffu;
+                    e0[i] = (int) (((seg << 5) + (uint32_t) lane) * VEC);
+                    bits[i] = vector_bits(seg);
+                    if (bits[i]) load_vec<T, VEC>(x + e0[i], xv[i]);
                 }
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
@@ -1042,7 +1100,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
 #pragma unroll
                     for (int j = 0; j < VEC; ++j) {
                         if (!(((bits[i] >> j) & 1u) && xv[i][j] >= thr_v && xv[i][j] <= FLT_MAX)) continue;
-                        const uint64_t key = make_key(xv[i][j], id0 + (uint32_t) ((ep * NT * NV + i * NT + tid) * VEC + j));
+                        const uint64_t key = make_key(xv[i][j], id0 + (uint32_t) (e0[i] + j));
                         if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (i * VEC + j);
                     }
                 }
@@ -1053,7 +1111,10 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                     uint32_t still = 0u;
                     for (uint32_t q = lost; q; q &= q - 1u) {
                         const int b = __ffs(q) - 1;
-                        const int e = (ep * NT * NV + (b / VEC) * NT + tid) * VEC + (b % VEC);
+                        int e = b % VEC;
+#pragma unroll
+                        for (int i = 0; i < NV; ++i)
+                            if (i == b / VEC) e += e0[i];
                         const uint64_t key = make_key(to_float(x[e]), id0 + (uint32_t) e);
                         if (key >= thr_key && !push(key, buf, sh, a.cap)) still |= 1u << b;
                     }
@@ -1282,7 +1343,7 @@ struct fns_b200_sampler {
 namespace {
 
 struct Plan {
-    int threads, slices, slice_len, cap, trigger, own_cap, vec, list_cap;
+    int threads, slices, slice_len, cap, trigger, own_cap, vec, list_cap, seg_cap;
     size_t smem_select;
 };
 
@@ -1338,8 +1399,9 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     pl.own_cap = 0;
     if (hist_bound > 0) pl.own_cap = round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4);
     pl.list_cap = pl.threads * 8;  // the sparse path lists at most 8 vectors per thread
-    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + (size_t) pl.own_cap * 8 +
-                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + 256 + sizeof(SelectShared) + 16;
+    pl.seg_cap = round_up(pl.slice_len / (32 * pl.vec) + 1, 256);  // room for the padding of the last group (<= 256 entries)
+    pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + 32 + (size_t) pl.own_cap * 8 +
+                     16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + (size_t) pl.seg_cap * 4 + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
 }
 
@@ -1446,6 +1508,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.trigger = pl.trigger;
     a.own_cap = pl.own_cap;
     a.list_cap = pl.list_cap;
+    a.seg_cap = pl.seg_cap;
     a.cand = s->cand;
     a.tickets = s->tickets;
     a.out_tokens = out_tokens;
