@@ -109,6 +109,7 @@ def run_b200(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = os.environ.get("FNS_NCCL_DEBUG", "WARN")  # no version banner on stdout: one JSON line
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --impl b200 needs a CUDA device: the sampler has no CPU path")
@@ -328,18 +329,28 @@ def batch1_latency(torch, dev, local):
     return res
 
 
+def host_threads() -> int:
+    """Every core this process may run on (launchers such as torchrun set OMP_NUM_THREADS=1, which is not that)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline(w, budget_s: float):
     """The CPU oracle (a port of the reference's sampler, not the product) on this host's cores, same rows."""
     from oracle.binding import Oracle
 
     o = Oracle()
+    cores = host_threads()
     x = w.logits
     t0, done, threads = time.time(), 0, 1
     n = min(32, w.rows)
     while time.time() - t0 < budget_s:
         lo = done % w.rows
         hi = min(w.rows, lo + n)
-        _, threads = o.sample_rows(x[lo:hi], w.params[lo:hi], 64, w.masks[lo:hi], w.history[lo:hi], w.history_len[lo:hi])
+        _, threads = o.sample_rows(x[lo:hi], w.params[lo:hi], 64, w.masks[lo:hi], w.history[lo:hi], w.history_len[lo:hi],
+                                   threads=cores)
         done += hi - lo
     dt = time.time() - t0
     return {"value": done / dt, "unit": "rows/s", "cores": threads, "kind": "port",
@@ -420,13 +431,14 @@ def run_reference(args):
     o = Oracle()
     sample_rows = 64
     w = wl.session_batch(seed=0, rows=sample_rows)
-    threads = 1
+    threads, cores = 1, host_threads()
     for _ in range(max(args.warmup, 1)):
-        _, threads = o.sample_rows(w.logits[:16], w.params[:16], 64, w.masks[:16], w.history[:16], w.history_len[:16])
+        _, threads = o.sample_rows(w.logits[:16], w.params[:16], 64, w.masks[:16], w.history[:16], w.history_len[:16],
+                                   threads=cores)
     K = min(args.steps, 40)
     t0 = time.time()
     for _ in range(K):
-        o.sample_rows(w.logits, w.params, 64, w.masks, w.history, w.history_len)
+        o.sample_rows(w.logits, w.params, 64, w.masks, w.history, w.history_len, threads=cores)
     dt = time.time() - t0
     value = sample_rows * K / dt
     line = {

@@ -1232,7 +1232,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     __syncthreads();
     FNS_PHASE(7)
     const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, reinterpret_cast<uint64_t *>(pj), 2 * a.k_cap, sh.sc, k, a.k_cap);
-    FNS_PHASE(9)
+    FNS_PHASE(10)
     draw_tail<NT>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
     FNS_PHASE(5)
 }
