@@ -307,36 +307,50 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         const double sum = *sum_slot;
         for (int j = tid; j < nk; j += NT) qj[j] = pj[j] / sum;
     }
-    __syncthreads();
+    volatile uint32_t * first_cut = &sc.hist[8];   // first j + 1 whose running probability reaches top_p
+    volatile uint32_t * first_low = &sc.hist[9];   // first j >= 1 whose probability is below min_p
+    volatile uint32_t * first_hit = &sc.hist[10];  // first j whose running weight exceeds the draw
     if (tid == 0) {
-        int keep = nk;
-        double cum = 0.0;
-        bool cut = false;
-        for (int j0 = 0; j0 < nk && !cut; j0 += 8) {
+        *first_cut = (uint32_t) nk;
+        *first_low = (uint32_t) nk;
+        *first_hit = 0xffffffffu;
+    }
+    __syncthreads();
+    if (tid == 0) {  // the running probability, left to right; the decisions on it are taken by everybody afterwards
+        double run = 0.0;
+        int j = 0;
+        for (; j + 8 <= nk; j += 8) {
             double t[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) t[u] = j0 + u < nk ? qj[j0 + u] : 0.0;
+            for (int u = 0; u < 8; ++u) t[u] = qj[j + u];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                if (cut || j0 + u >= nk) continue;
-                cum += t[u];
-                if (cum >= p.top_p) {
-                    keep = j0 + u + 1;
-                    cut = true;
-                }
+                run += t[u];
+                qj[j + u] = run;
             }
         }
-        if (p.min_p > 0.0f) {
-            int m = 1;
-            while (m < keep && pj[m] >= (double) p.min_p) ++m;
-            keep = m;
+        for (; j < nk; ++j) {
+            run += qj[j];
+            qj[j] = run;
         }
-        const double wsum = acc[keep - 1];
-        const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
-        int pick = keep - 1;
-        for (int j = 0; j < keep; ++j)
-            if (u < acc[j]) { pick = j; break; }
-        *out_token = key_id(sorted[pick]);
+    }
+    __syncthreads();
+    // `cum >= top_p` first holds at the smallest such j (the sums never decrease); min_p keeps the longest prefix of
+    // the rest whose probabilities reach it
+    for (int j = tid; j < nk; j += NT) {
+        if (qj[j] >= (double) p.top_p) atomicMin(const_cast<uint32_t *>(first_cut), (uint32_t) j + 1u);
+        if (p.min_p > 0.0f && j >= 1 && !(pj[j] >= (double) p.min_p)) atomicMin(const_cast<uint32_t *>(first_low), (uint32_t) j);
+    }
+    __syncthreads();
+    const int keep = (int) min(*first_cut, *first_low);
+    const double wsum = acc[keep - 1];
+    const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
+    for (int j = tid; j < keep; j += NT)
+        if (u < acc[j]) atomicMin(const_cast<uint32_t *>(first_hit), (uint32_t) j);
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t hit = *first_hit;
+        *out_token = key_id(sorted[hit == 0xffffffffu ? keep - 1 : (int) hit]);
     }
 }
 
@@ -401,7 +415,10 @@ __device__ __forceinline__ float value_in_word(uint32_t w, const __nv_bfloat16 *
 #else
 #define FNS_MINBLOCKS(NT) (1024 / NT)
 #endif
-template <typename T, int VEC, int NT>
+// DIRECT: the plan promises at most two groups per slice (slice_len <= 2 * NT * 16): both stay in registers until
+// the bound is final and the candidates are taken straight from there (no running bound, no flags, nothing read
+// twice).  The slices of a single row are like that.
+template <typename T, int VEC, int NT, bool DIRECT>
 __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectArgs a) {
     constexpr int NV = kEpochElems / VEC;                    // vectors per thread per epoch
     constexpr int FPE = NV < 4 ? NV : 4;                     // flag bits per thread and epoch
@@ -732,8 +749,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         }
         return false;
     };
-    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
-        float vmx[NV], emax = -INFINITY;
+    // The maxima of the NV vectors of a group (vmx) and of the whole group (returned; +inf if an allowed element is).
+    auto group_max = [&](float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain, float (&vmx)[NV]) -> float {
+        float emax = -INFINITY;
         if (plain) {  // every element counts (history ids too: see taint)
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
@@ -762,6 +780,11 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 emax = fmaxf(emax, m);
             }
         }
+        return emax;
+    };
+    auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
+        float vmx[NV];
+        float emax = group_max(xv, mb, plain, vmx);
         constexpr int EPW = 64 / FPE;  // epochs per flag word
         if (__builtin_expect(!(emax <= FLT_MAX), 0)) {
             // +inf among the allowed elements: never a candidate (src/kernels.cu:629-639).  The epoch is left to
@@ -834,6 +857,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     };
     constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
     const bool sparse = n_av <= min(NT * LPT, a.list_cap);
+    float xa[NV][VEC], xb[NV][VEC];  // the two groups in flight
+    uint32_t ma[NV], mb[NV];
+    bool pa = false, pb = false;
     if (sparse) {
         // 3a. Few allowed vectors (a grammar mask that admits little): no epochs.  The allowed vectors are listed
         // from the bit set, every thread requests all of its (at most LPT) at once, and after ONE memory round
@@ -900,14 +926,44 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 if (!__syncthreads_or(lost != 0u)) break;
             }
         }
-    } else {
-        float xa[NV][VEC], xb[NV][VEC];
+    } else if constexpr (DIRECT) {
 #pragma unroll
         for (int i = 0; i < NV; ++i)
 #pragma unroll
             for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
-        uint32_t ma[NV], mb[NV];
-        bool pa = false, pb = false;
+        if (n_groups > 0) pa = issue(0, xa, ma);
+        if (n_groups > 1) pb = issue(1, xb, mb);
+        if (t_mine) {
+            copy_word_wait();
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if ((t_mine >> u) & 1u) publish_taint(t_base + ((t_pre >> (8 * u)) & 255u));
+        }
+        if (n_own > 0) {  // uniform
+            __syncthreads();
+            taint_w = taint[tid];
+        }
+        auto take_max = [&](int g, float (&xv)[NV][VEC], uint32_t (&mv)[NV], bool plain) {
+            float vmx[NV];
+            float emax = group_max(xv, mv, plain, vmx);
+            if (!(emax <= FLT_MAX)) {  // +inf among the allowed elements: the largest finite one, the slow way
+                emax = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const uint32_t bits = vector_bits(my_entries[g * (kWarps * NV) + i] & 0x7fffu);
+                    if (bits) emax = fmaxf(emax, vector_max<VEC>(xv[i], bits));
+                }
+            }
+            tmax = fmaxf(tmax, emax);
+        };
+        if (n_groups > 0) take_max(0, xa, ma, pa);
+        if (n_groups > 1) take_max(1, xb, mb, pb);
+        done = n_groups;
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) xa[i][j] = xb[i][j] = 0.0f;
         if (n_groups > 0) pa = issue(0, xa, ma);
 #pragma unroll 1
         for (int g = 0; g < n_groups; g += 2) {
@@ -1033,7 +1089,28 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
         // careful way walks every epoch instead, one per round, with a vote after each.
         bool listed = true;
-        if (!careful) {
+        if (DIRECT && !careful && !sparse) {
+            if constexpr (DIRECT) {
+            auto offer_group = [&](int g, float (&xv)[NV][VEC]) {
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const uint32_t seg = my_entries[g * (kWarps * NV) + i] & 0x7fffu;
+                        const uint32_t bits = vector_bits(seg);  // (the bit set: history ids are out, also in a whole segment)
+                        if (!bits) continue;
+                        const uint32_t e = ((seg << 5) + (uint32_t) lane) * VEC;
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) {
+                            if (!(((bits >> j) & 1u) && xv[i][j] >= thr_v && xv[i][j] <= FLT_MAX)) continue;
+                            const uint64_t key = make_key(xv[i][j], id0 + e + (uint32_t) j);
+                            if (k == 1) best = key > best ? key : best;
+                            else if (key >= thr_key) push(key, buf, sh, a.cap);
+                        }
+                    }
+                };
+                if (n_groups > 0) offer_group(0, xa);
+                if (n_groups > 1) offer_group(1, xb);
+            }
+        } else if (!careful) {
             // one reservation per warp: a prefix sum over the lanes' flag counts
             const int mine_n = (__popcll(f0) + __popcll(f1)) * VPF;
             int upto = mine_n;
@@ -1409,9 +1486,9 @@ size_t final_smem(int lists, int list_len, int k_cap) {
     return (size_t) lists * list_len * 8 + (size_t) k_cap * 8 * 4 + sizeof(FinalShared) + 16;
 }
 
-template <typename T, int VEC, int NT>
-cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
-    auto kern = k_select<T, VEC, NT>;
+template <typename T, int VEC, int NT, bool DIRECT>
+cudaError_t launch_select_d(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
+    auto kern = k_select<T, VEC, NT, DIRECT>;
     static bool configured[64] = {};  // per device: the opt-in to large dynamic shared memory is sticky
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1422,6 +1499,12 @@ cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStr
     }
     kern<<<dim3((unsigned) a.slices, (unsigned) rows), NT, smem, st>>>(a);
     return cudaGetLastError();
+}
+
+template <typename T, int VEC, int NT>
+cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
+    return a.slice_len <= 2 * NT * kEpochElems ? launch_select_d<T, VEC, NT, true>(a, rows, smem, st)
+                                                : launch_select_d<T, VEC, NT, false>(a, rows, smem, st);
 }
 
 template <int NT>
