@@ -207,6 +207,7 @@ __device__ void block_rank_sort(const uint64_t * sel, int m, uint64_t * out) {
     for (int i = threadIdx.x; i < m; i += NT) {
         const uint64_t key = sel[i];
         int rank = 0;
+#pragma unroll 8
         for (int j = 0; j < m; ++j) rank += sel[j] > key ? 1 : 0;
         out[rank] = key;
     }
@@ -220,6 +221,7 @@ __device__ int block_rank_select(const uint64_t * buf, int n, int k, uint64_t * 
     for (int i = threadIdx.x; i < n; i += NT) {
         const uint64_t key = buf[i];
         int rank = 0;
+#pragma unroll 8
         for (int j = 0; j < n; ++j) rank += buf[j] > key ? 1 : 0;
         if (rank < k) out[rank] = key;
     }

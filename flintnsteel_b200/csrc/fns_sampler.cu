@@ -190,12 +190,23 @@ __device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, u
         sc.or_lo = 0u;
     }
     __syncthreads();
+    // (the witnesses are first copied side by side, so that the counting loop is one flat, unrolled walk)
+    uint64_t * wit = spare;  // n_wit <= spare_len is checked below; the scratch list is written only afterwards
+    const bool flat = n_wit <= spare_len;
+    if (flat)
+        for (int i = tid; i < n_wit; i += NT) wit[i] = buf[(i / depth) * len + (i % depth)];
+    __syncthreads();
     for (int i = tid; i < n_wit; i += NT) {
         const uint64_t key = buf[(i / depth) * len + (i % depth)];
         if (key == 0ull) continue;
         int rank = 0;
-        for (int l = 0; l < lists; ++l)
-            for (int d = 0; d < depth; ++d) rank += buf[l * len + d] > key ? 1 : 0;
+        if (flat) {
+#pragma unroll 8
+            for (int j = 0; j < n_wit; ++j) rank += wit[j] > key ? 1 : 0;
+        } else {
+            for (int l = 0; l < lists; ++l)
+                for (int d = 0; d < depth; ++d) rank += buf[l * len + d] > key ? 1 : 0;
+        }
         if (rank == k - 1) {
             sc.or_hi = (uint32_t) (key >> 32);
             sc.or_lo = (uint32_t) key;
@@ -1447,7 +1458,9 @@ int fail_cuda(fns_b200_sampler * s, cudaError_t e, const char * where) {
 // (512 threads) of them; the slices' lists of one row must fit the merge (kMaxMergeKeys).
 bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
     const int k_cap = s->k_cap;
-    pl.threads = s->force_threads > 0 ? s->force_threads : (s->force_slices > 0 ? 256 : (rows >= s->sm_count ? 512 : 256));
+    // (a handful of rows: fewer, larger slices keep the merge of the slices' lists short)
+    pl.threads = s->force_threads > 0 ? s->force_threads
+                                      : (s->force_slices > 0 ? 256 : ((rows >= s->sm_count || rows <= 4) ? 512 : 256));
     const int epoch = pl.threads * kEpochElems;
     const int max_slice_len = (pl.threads == 256 ? 16 : 32) * epoch;
     const int min_slices = (vocab + max_slice_len - 1) / max_slice_len;
@@ -1456,7 +1469,7 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     if (min_slices > max_slices) return false;
     int want;
     if (s->force_slices > 0) want = s->force_slices;
-    else if (pl.threads == 512) want = 1;
+    else if (pl.threads == 512 && rows >= s->sm_count) want = 1;
     else want = (s->sm_count * 4 + rows - 1) / rows;
     const int by_len = (vocab + epoch - 1) / epoch;  // no slice shorter than one epoch
     if (want > by_len) want = by_len;
