@@ -4,19 +4,22 @@
 //
 //   k_select   grid (slices, rows); one block per (row, slice).  With many rows a slice is the whole row and a
 //              block has 512 threads (two per SM: 296 rows in flight at once); with few rows a row is cut into
-//              slices of 256-thread blocks so that the whole GPU works on it.  Per slice:
-//                1. the grammar bitmask and the penalty history are folded into a shared-memory bit set;
-//                2. pass 1 streams the logits once with 128-bit coalesced loads, two epochs in flight, and keeps
-//                   nothing but maxima: per thread the maximum seen, per vector group one flag "reaches the
-//                   running bound".  The bound is a value that at least k elements of the slice are known to
-//                   reach, found with warp-wide max reductions over the threads' maxima; nothing is appended,
-//                   nothing is compared element by element, regions the bit set masks out are never loaded;
-//                3. pass 2 reads the flagged groups again (L2) and appends the elements that reach the final
-//                   bound (about k to 2k of them) to a shared buffer; penalised candidates join them;
-//                4. the best k of the buffer, sorted, are the slice's answer (rank by counting, or radix select
-//                   when an adversarial input has filled the buffer; the buffer is compacted whenever it fills,
-//                   so any input is handled exactly);
-//                5. the last block of a row to finish (a ticket, no waiting) merges the slices' lists and does
+//              slices so that the whole GPU works on it.  Per slice:
+//                1. the grammar bitmask becomes a shared-memory bit set and a list of the 512-byte segments that
+//                   have an allowed id; every history id clears its bit, and the thread that clears it owns the id;
+//                2. pass 1 streams the listed segments once with 128-bit coalesced loads, two groups in flight,
+//                   and keeps nothing but maxima: per thread the maximum seen, per vector group one flag "reaches
+//                   the running bound".  The bound is a value that at least k elements of the slice are known to
+//                   reach, found from the threads' maxima alone; nothing is appended, nothing is compared element
+//                   by element, and what the mask excludes is never loaded;
+//                3. the bound is tightened to (nearly) the k-th largest thread maximum with a counted bisection;
+//                4. the few flagged vectors of the few threads whose maximum reaches the bound are read again
+//                   (L2) and their elements that reach it (about k of them) go to a shared buffer; the penalised
+//                   history ids join them;
+//                5. the best k of the buffer, sorted, are the slice's answer (rank by counting; if many equal
+//                   values overflow the buffer, everything is offered again with compaction, so any input is
+//                   handled exactly);
+//                6. the last block of a row to finish (a ticket, no waiting) merges the slices' lists and does
 //                   the candidate softmax, top-p / min-p cut, temperature weights and Philox draw.
 //              Replaces k_topk_part (src/kernels.cu:624-648, which rescans its slice k times), k_presence_apply /
 //              _col (src/kernels.cu:724-742, which rewrite the whole row) and k_sample (src/kernels.cu:671-721)
@@ -59,8 +62,8 @@ __device__ unsigned g_rowphase[1024][16];   // last launch: cycles per phase of 
 
 constexpr int kMaxMergeKeys = 8192;   // k_finalize holds the lists of one row in shared memory
 constexpr int kMaxSlices = 128;
-constexpr int kEpochElems = 16;       // elements per thread and epoch
-// epochs per slice: at most 16 for 256-thread blocks and 32 for 512-thread blocks (64 flag bits per thread)
+constexpr int kEpochElems = 16;       // elements per thread and group (a slice is at most 16 groups of a 256-thread
+                                      // block's elements, or 32 of a 512-thread block's: 128 flag bits per thread)
 constexpr int kMaxWarps = 16;
 constexpr int kRankSelectMax = 384;   // candidate sets up to this size are ranked by counting
 
@@ -80,7 +83,7 @@ struct SelectArgs {
     fns_b200_params p0;
     int k_cap;
     int slices;
-    int slice_len;   // a multiple of the block's epoch
+    int slice_len;   // a multiple of threads * 16 elements
     int cap;         // candidate buffer entries (>= 4 * k_cap)
     int trigger;     // compact when the buffer holds this many
     int own_cap;     // entries of the list of owned history ids (a multiple of 4), 0: no penalties
@@ -421,26 +424,19 @@ __device__ __forceinline__ float value_in_word(uint32_t w, const __nv_bfloat16 *
     return __uint_as_float((reinterpret_cast<uintptr_t>(p) & 2) ? (w & 0xffff0000u) : (w << 16));
 }
 
-#ifdef FNS_LB1
-#define FNS_MINBLOCKS(NT) 1
-#else
-#define FNS_MINBLOCKS(NT) (1024 / NT)
-#endif
 // DIRECT: the plan promises at most two groups per slice (slice_len <= 2 * NT * 16): both stay in registers until
 // the bound is final and the candidates are taken straight from there (no running bound, no flags, nothing read
 // twice).  The slices of a single row are like that.
 template <typename T, int VEC, int NT, bool DIRECT>
-__global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectArgs a) {
-    constexpr int NV = kEpochElems / VEC;                    // vectors per thread per epoch
-    constexpr int FPE = NV < 4 ? NV : 4;                     // flag bits per thread and epoch
+__global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
+    constexpr int NV = kEpochElems / VEC;                    // vectors per thread per group
+    constexpr int FPE = NV < 4 ? NV : 4;                     // flag bits per thread and group
     constexpr int VPF = NV / FPE;                            // vectors per flag bit (a "group")
     constexpr int TS = 2 * NT;                               // slots of the occurrence-count table
     constexpr int kTShift = NT == 512 ? 22 : 23;             // 32 - log2(TS)
     constexpr uint32_t kNoKey = 0xffffffffu;
-    constexpr int kEpoch = NT * kEpochElems;                 // elements per block per epoch
     constexpr int kWarps = NT / 32;
     constexpr uint32_t kVecBits = VEC == 32 ? 0xffffffffu : (1u << VEC) - 1u;
-    constexpr int kWordsPerVec = NT * VEC / 32;              // bit-set words between two vectors of one thread
     static_assert(32 * FPE <= 128, "two 64-bit flag words hold the longest slice");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -490,8 +486,8 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     }
 
     // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
-    // streaming loop needs no bounds handling.  Every warp also counts the vectors that have an allowed element
-    // and notes which epochs have any; the block adds these up after the barrier, without atomics.
+    // streaming loop needs no bounds handling.  Every warp also counts its allowed elements; the block adds these
+    // up after the barrier, without atomics.
     auto vector_units = [](uint32_t m) -> uint32_t {  // one bit per vector: the OR of its mask bits
         if constexpr (VEC == 1) return m;
         if constexpr (VEC == 4) return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x11111111u;
@@ -617,7 +613,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     // slice reads the list; it stays in L2).
     int n_own = 0;
     uint32_t t_base = 0u, t_pre = 0u, t_mine = 0u;  // this thread's list slots of the first round
-    // A history logit may become its thread's maximum in an epoch that is streamed without the bit set.  Such a
+    // A history logit may become its thread's maximum in a group that is streamed without the bit set.  Such a
     // maximum must not count as a witness for the bound, so every owner records the logit in taint[] of the thread
     // that streams the element: a thread whose maximum does not exceed its taint is left out of the bound.
     auto publish_taint = [&](uint32_t slot) {
@@ -673,6 +669,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             }
         }
     }
+    FNS_PHASE(12)
     __syncthreads();
     if (use_hist) n_own = (int) sh.n_own;
     // The row's ragged end: the elements of a last, partial vector are taken out of the bit set here, so that the
@@ -796,9 +793,9 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     auto reduce = [&](int ep, float (&xv)[NV][VEC], uint32_t (&mb)[NV], bool plain) {
         float vmx[NV];
         float emax = group_max(xv, mb, plain, vmx);
-        constexpr int EPW = 64 / FPE;  // epochs per flag word
+        constexpr int EPW = 64 / FPE;  // groups per flag word
         if (__builtin_expect(!(emax <= FLT_MAX), 0)) {
-            // +inf among the allowed elements: never a candidate (src/kernels.cu:629-639).  The epoch is left to
+            // +inf among the allowed elements: never a candidate (src/kernels.cu:629-639).  The group is left to
             // pass 2, which looks at every element, and adds nothing to this thread's maximum.
             const uint64_t every = (1ull << FPE) - 1ull;
             if (ep < EPW) f0 |= every << (ep * FPE);
@@ -806,22 +803,18 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
             emax = -INFINITY;
         }
         tmax = fmaxf(tmax, emax);
-#ifdef FNS_X_NOREFRESH
-        if (bounded && done == 0)
-#else
         if (__builtin_expect(bounded && done == next_refresh, 0))
-#endif
         {
             if (done == 0 && n_own > 0) {  // uniform: the owners have published their taint before their first reduce
                 __syncthreads();
                 taint_w = taint[tid];
             }
             thr_v = block_bound<NT>(clean_max(), thr_v, lanes_per_group, done == 0, k == 1, sh);
-            next_refresh = done == 0 ? 1 : (done == 1 ? 3 : -1);  // after epochs 1, 2 and 4, then not before the end
+            next_refresh = done == 0 ? 1 : (done == 1 ? 3 : -1);  // after groups 1, 2 and 4, then not before the end
         }
         ++done;
         if (__builtin_expect(emax >= thr_v, 0)) {
-            uint64_t hb = 0ull;  // the groups of this epoch that reach the bound
+            uint64_t hb = 0ull;  // the vector groups of this group that reach the bound
 #pragma unroll
             for (int g = 0; g < FPE; ++g) {
                 bool q = false;
@@ -872,7 +865,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
     uint32_t ma[NV], mb[NV];
     bool pa = false, pb = false;
     if (sparse) {
-        // 3a. Few allowed vectors (a grammar mask that admits little): no epochs.  The allowed vectors are listed
+        // 3a. Few allowed vectors (a grammar mask that admits little): no groups.  The allowed vectors are listed
         // from the bit set, every thread requests all of its (at most LPT) at once, and after ONE memory round
         // trip the bound is known and the candidates are appended straight from registers.
         for (int w = tid; w < a.slice_len / 32; w += NT) {
@@ -1098,7 +1091,7 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
         FNS_PHASE(6)
         // (c) The flagged groups.  Their vectors go on a work list that the whole block then shares: one vector per
         // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
-        // careful way walks every epoch instead, one per round, with a vote after each.
+        // careful way walks every group instead, one per round, with a vote after each.
         bool listed = true;
         if (DIRECT && !careful && !sparse) {
             if constexpr (DIRECT) {
@@ -1172,7 +1165,6 @@ __global__ void __launch_bounds__(NT, FNS_MINBLOCKS(NT)) k_select(const SelectAr
                 uint32_t bits[NV], lost = 0u;  // lost: elements of this round that found the buffer full
                 int e0[NV];                    // first element of each vector of this round
                 float xv[NV][VEC];
-#pragma unroll
                 uint32_t en[NV];
                 entries_of(g, en);
 #pragma unroll
@@ -1436,11 +1428,6 @@ struct Plan {
 };
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
-int next_pow2(int x) {
-    int p = 1;
-    while (p < x) p <<= 1;
-    return p;
-}
 
 int fail(fns_b200_sampler * s, int code, const char * what) {
     if (s) std::snprintf(s->msg, sizeof s->msg, "%s", what);
@@ -1454,7 +1441,7 @@ int fail_cuda(fns_b200_sampler * s, cudaError_t e, const char * where) {
 // Launch geometry.  With at least one row per SM a row is one slice and a block has 512 threads: two blocks fit
 // an SM, so up to 2 * SMs rows stream at once, and setup, history and draw are paid once per row.  With fewer
 // rows a row is cut into slices of 256-thread blocks, about four per SM in total, so that the whole GPU works on
-// the call.  A slice is a whole number of epochs (16 elements per thread) and at most 16 (256 threads) or 32
+// the call.  A slice is a whole number of threads * 16 elements and at most 16 (256 threads) or 32
 // (512 threads) of them; the slices' lists of one row must fit the merge (kMaxMergeKeys).
 bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
     const int k_cap = s->k_cap;
