@@ -381,7 +381,7 @@ def test_results_do_not_depend_on_the_launch_geometry(dev):
         assert np.array_equal(t, base_t) and np.array_equal(c, base_c), slices
 
 
-@pytest.mark.parametrize("n", [1, 2, 31, 32, 33, 127, 1187, 1188, 4097, 65_537])
+@pytest.mark.parametrize("n", [1, 2, 31, 32, 33, 127, 1187, 1188, 4000, 4097, 20_000, 65_537])
 def test_small_and_ragged_vocabularies(dev, oracle, n):
     g = wl.rng(n)
     rows = 5
