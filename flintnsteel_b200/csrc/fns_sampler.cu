@@ -1438,16 +1438,16 @@ int fail_cuda(fns_b200_sampler * s, cudaError_t e, const char * where) {
     return FNS_B200_ERR_CUDA;
 }
 
-// Launch geometry.  With at least one row per SM a row is one slice and a block has 512 threads: two blocks fit
-// an SM, so up to 2 * SMs rows stream at once, and setup, history and draw are paid once per row.  With fewer
-// rows a row is cut into slices of 256-thread blocks, about four per SM in total, so that the whole GPU works on
-// the call.  A slice is a whole number of threads * 16 elements and at most 16 (256 threads) or 32
-// (512 threads) of them; the slices' lists of one row must fit the merge (kMaxMergeKeys).
-bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
+// Launch geometry.  A block has 512 threads (two fit an SM).  From five rows on a row is one slice: setup, history
+// and draw are paid once per row and there is nothing to merge; this measured faster than any cut at every batch
+// size from 5 to 1024 rows.  Up to four rows are cut into slices of one group per thread (8,192 elements), so that
+// many SMs share the row, and the last block to finish merges the slices' lists.  A slice is a whole number of
+// threads * 16 elements and at most 16 (256 threads) or 32 (512 threads) of them; the slices' lists of one row must
+// fit the merge (kMaxMergeKeys).
+bool make_plan_for(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, bool whole_rows,
+                   Plan & pl) {
     const int k_cap = s->k_cap;
-    // (a handful of rows: fewer, larger slices keep the merge of the slices' lists short)
-    pl.threads = s->force_threads > 0 ? s->force_threads
-                                      : (s->force_slices > 0 ? 256 : ((rows >= s->sm_count || rows <= 4) ? 512 : 256));
+    pl.threads = s->force_threads > 0 ? s->force_threads : (s->force_slices > 0 ? 256 : 512);
     const int epoch = pl.threads * kEpochElems;
     const int max_slice_len = (pl.threads == 256 ? 16 : 32) * epoch;
     const int min_slices = (vocab + max_slice_len - 1) / max_slice_len;
@@ -1456,7 +1456,7 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     if (min_slices > max_slices) return false;
     int want;
     if (s->force_slices > 0) want = s->force_slices;
-    else if (pl.threads == 512 && rows >= s->sm_count) want = 1;
+    else if (whole_rows) want = 1;
     else want = (s->sm_count * 4 + rows - 1) / rows;
     const int by_len = (vocab + epoch - 1) / epoch;  // no slice shorter than one epoch
     if (want > by_len) want = by_len;
@@ -1480,6 +1480,12 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
     pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + 32 + (size_t) pl.own_cap * 8 +
                      16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + (size_t) pl.seg_cap * 4 + sizeof(SelectShared) + 16;
     return pl.smem_select <= 200 * 1024;
+}
+
+bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
+    const bool whole_rows = s->force_threads <= 0 && s->force_slices <= 0 && rows > 4;
+    if (whole_rows && make_plan_for(s, dtype, vocab, rows, hist_bound, aligned, true, pl)) return true;
+    return make_plan_for(s, dtype, vocab, rows, hist_bound, aligned, false, pl);  // (a long history may not fit a whole row)
 }
 
 size_t final_smem(int lists, int list_len, int k_cap) {
