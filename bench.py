@@ -107,9 +107,17 @@ def run_b200(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    json_fd = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = os.environ.get("FNS_NCCL_DEBUG", "WARN")  # no version banner on stdout: one JSON line
+        # stdout carries ONE JSON line: NCCL's banner and anything else a library prints go to stderr
+        if "FNS_NCCL_DEBUG" in os.environ:
+            os.environ["NCCL_DEBUG"] = os.environ["FNS_NCCL_DEBUG"]
+        else:
+            os.environ.pop("NCCL_DEBUG", None)
+        sys.stdout.flush()
+        json_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --impl b200 needs a CUDA device: the sampler has no CPU path")
@@ -278,7 +286,12 @@ def run_b200(args):
         if rank == 0:
             result["vocab_sharded"] = vs
     if rank == 0:
-        print(json.dumps(result))
+        line = json.dumps(result)
+        if json_fd is None:
+            print(line)
+        else:
+            sys.stdout.flush()
+            os.write(json_fd, (line + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 
