@@ -272,8 +272,91 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         if (tid == 0) *out_token = key_id(sorted[0]);
         return;
     }
-    // The two exponentials of a candidate go to different halves of the block, so they run side by side.
     const double v0 = (double) key_value(sorted[0]);
+    if (nk <= 64 && NT >= 160) {
+        // The usual case, at most 64 candidates: after the exponentials (threads 0-63 and 64-127, side by side, the
+        // uniform on thread 128) ONE warp does the rest without another block barrier.  Lane 0 walks the running
+        // sums left to right, as the reference adds; every lane then holds candidates j = lane and lane + 32, and
+        // the three decisions (top-p cut, min-p cut, inverse-CDF hit) are the first set bits of ballots.
+        if (tid < 128) {
+            const int j = tid & 63;
+            if (j < nk) {
+                const double d = (double) key_value(sorted[j]) - v0;
+                if (tid < 64) pj[j] = exp(d);
+                else acc[j] = exp(d / p.temperature);
+            }
+        } else if (tid == 128) {
+            reinterpret_cast<volatile double *>(&sc.hist[0])[1] = philox_uniform(p.seed, p.counter);
+        }
+        __syncthreads();
+        if (tid >= 32) return;
+        const int lane = tid, hi = tid + 32;
+        double sum = 0.0;
+        if (lane == 0) {
+            double run = 0.0;
+            int j = 0;
+            for (; j + 4 <= nk; j += 4) {
+                double a4[4], w4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    a4[u] = pj[j + u];
+                    w4[u] = acc[j + u];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    sum += a4[u];
+                    run += w4[u];
+                    acc[j + u] = run;
+                }
+            }
+            for (; j < nk; ++j) {
+                sum += pj[j];
+                run += acc[j];
+                acc[j] = run;
+            }
+        }
+        __syncwarp();
+        sum = __shfl_sync(kFull, sum, 0);
+        const double p0 = lane < nk ? pj[lane] : 0.0, p1 = hi < nk ? pj[hi] : 0.0;
+        if (lane < nk) qj[lane] = p0 / sum;
+        if (hi < nk) qj[hi] = p1 / sum;
+        __syncwarp();
+        if (lane == 0) {
+            double run = 0.0;
+            int j = 0;
+            for (; j + 4 <= nk; j += 4) {
+                double q4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) q4[u] = qj[j + u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    run += q4[u];
+                    qj[j + u] = run;
+                }
+            }
+            for (; j < nk; ++j) {
+                run += qj[j];
+                qj[j] = run;
+            }
+        }
+        __syncwarp();
+        auto first_of = [&](bool lo_bit, bool hi_bit, int none) -> int {  // index of the first candidate with the property
+            const uint32_t b0 = __ballot_sync(kFull, lo_bit), b1 = __ballot_sync(kFull, hi_bit);
+            return b0 ? __ffs(b0) - 1 : (b1 ? 31 + __ffs(b1) : none);
+        };
+        const int cut = first_of(lane < nk && qj[lane] >= (double) p.top_p, hi < nk && qj[hi] >= (double) p.top_p, nk - 1) + 1;
+        int keep = cut;
+        if (p.min_p > 0.0f) {
+            const int low = first_of(lane >= 1 && lane < nk && !(p0 >= (double) p.min_p), hi < nk && !(p1 >= (double) p.min_p), nk);
+            keep = low < keep ? low : keep;
+        }
+        const double wsum = acc[keep - 1];
+        const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
+        const int pick = first_of(lane < keep && u < acc[lane], hi < keep && u < acc[hi], keep - 1);
+        if (lane == 0) *out_token = key_id(sorted[pick]);
+        return;
+    }
+    // More candidates: the two exponentials of a candidate go to different halves of the block.
     {
         const bool second = tid >= NT / 2;
         for (int j = second ? tid - NT / 2 : tid; j < nk; j += NT / 2) {
