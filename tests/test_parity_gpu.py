@@ -501,6 +501,23 @@ def test_history_of_the_largest_logits_with_repeats_and_every_penalty_sign(dev, 
     check_against_oracle(oracle, w, tokens, cands)
 
 
+def test_history_too_long_for_a_whole_row_falls_back_to_slices(dev, oracle):
+    """60,000 history ids per row do not fit the shared memory of a whole-row block: the plan cuts the rows."""
+    g = wl.rng(5)
+    rows, n, h = 6, 151_936, 60_000
+    x = wl.gaussian_logits(g, rows, n, 2.5)
+    hist = g.integers(0, n, size=(rows, h), dtype=np.int32)
+    hlen = np.full(rows, h, np.int32)
+    hlen[1] = 12_345
+    p = make_params(rows, temperature=0.8, top_k=50, top_p=0.95, repetition=1.1, presence=0.4, frequency=0.2, seed=3)
+    w = wl.Workload("long_history", x, p, None, hist, hlen)
+    s = Sampler(0, max_rows=rows, max_vocab=n, k_cap=64, max_history=h)
+    assert s.plan(0, n, rows, h)["slices"] > 1
+    s.close()
+    tokens, cands = run_rows(w, dev, max_history=h)
+    check_against_oracle(oracle, w, tokens, cands)
+
+
 def test_whole_row_blocks_at_batch_sizes_around_the_sm_count(dev, oracle):
     """At 148 rows and more a row is one 512-thread block; just below, rows are cut into slices."""
     for rows in (147, 149, 300):
