@@ -87,7 +87,7 @@ struct SelectArgs {
     int cap;         // candidate buffer entries (>= 4 * k_cap)
     int trigger;     // compact when the buffer holds this many
     int own_cap;     // entries of the list of owned history ids (a multiple of 4), 0: no penalties
-    int list_cap;    // entries of the allowed-vector list of a sparse slice
+    int list_cap;    // entries of the work list of the second pass
     int seg_cap;     // segments of a slice (32 vectors each), a multiple of 4
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
@@ -101,13 +101,12 @@ struct SelectShared {
     uint64_t thr_key;     // the exact k-th best key of the buffer at its last compaction
     uint32_t n_cand;      // append cursor; may run past cap (the excess was not stored: see `lost`)
     uint32_t n_own;       // history ids of the slice that the mask allows, each once
-    uint32_t n_vl;        // cursor of the allowed-vector list
+    uint32_t n_vl;        // cursor of the work list
     uint32_t n_seg;       // segments with an allowed element
     int keep;
     int is_last;
     __align__(16) float warp_bound[kMaxWarps];  // per warp: a value that r of its lanes have reached
     uint32_t warp_top[kMaxWarps];               // per warp: its largest thread maximum (as an order word)
-    uint32_t red_cnt[kMaxWarps];                // per warp: vectors with an allowed element
     uint64_t red[kMaxWarps];
 };
 
@@ -540,7 +539,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     uint32_t * own = eff + a.slice_len / 32 + 8;  // (8 zero words follow the bit set: the bits of the list's padding)
     uint32_t * oval = own + a.own_cap;
     float4 * lut = reinterpret_cast<float4 *>(oval + a.own_cap);
-    uint32_t * vlist = reinterpret_cast<uint32_t *>(lut + 16);  // [list_cap] allowed vectors of a sparse slice
+    uint32_t * vlist = reinterpret_cast<uint32_t *>(lut + 16);  // [list_cap] work list of the second pass: vectors to read again
     uint32_t * tkey = vlist + a.list_cap;                       // [TS] in-slice offsets whose occurrences are counted
     uint32_t * tcnt = tkey + TS;                                // [TS]
     uint32_t * taint = tcnt + TS;                               // [NT] per thread: its largest history logit
@@ -571,12 +570,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     // 1. The slice's bit set: bit e = element lo + e is allowed.  Bits past the end of the row are 0, so the
     // streaming loop needs no bounds handling.  Every warp also counts its allowed elements; the block adds these
     // up after the barrier, without atomics.
-    auto vector_units = [](uint32_t m) -> uint32_t {  // one bit per vector: the OR of its mask bits
-        if constexpr (VEC == 1) return m;
-        if constexpr (VEC == 4) return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x11111111u;
-        m |= m >> 4;
-        return (m | (m >> 1) | (m >> 2) | (m >> 3)) & 0x01010101u;
-    };
     const int words = (n_s + 31) >> 5;
     if (tid == 0) {
         sh.n_cand = 0u;
@@ -608,7 +601,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         const uint32_t below = (1u << lane) - 1u;
         const uint32_t tail = (n_s & 31) ? (1u << (n_s & 31)) - 1u : 0xffffffffu;
         const bool wide = WPS >= 4 && mrow && (reinterpret_cast<uintptr_t>(mrow) & 15u) == 0;
-        uint32_t cnt = 0u;
 #pragma unroll 1
         for (int s0 = 0; s0 < slice_segs; s0 += NT * SU) {  // one round for slices up to 2048 * NT / 512 segments
             uint32_t mw[SU][WPS];
@@ -643,7 +635,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                         if (seg * WPS + q == words - 1) mw[u][q] &= tail;
                         any |= mw[u][q];
                         all &= mw[u][q];
-                        cnt += (uint32_t) __popc(mw[u][q]);
                         eff[seg * WPS + q] = mw[u][q];
                     }
                 }
@@ -665,8 +656,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 at += (uint32_t) __popc(lead[u]);
             }
         }
-        cnt = __reduce_add_sync(kFull, cnt);
-        if (lane == 0) sh.red_cnt[warp] = cnt;
     }
     const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
     const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
@@ -674,12 +663,8 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
     const int n_pen = n_hist + (a.draft ? col : 0);
     uint64_t best = 0ull;      // k == 1: this thread's best key
-    uint32_t lost = 0u;        // elements of the current round that found the buffer full
     __syncthreads();
     FNS_PHASE(0)
-    int n_av = 0;              // allowed elements (so at most that many vectors with one), before the history is taken out
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) n_av += (int) sh.red_cnt[w];
     const int n_seg = (int) sh.n_seg;
     const int n_groups = (n_seg + kWarps * NV - 1) / (kWarps * NV);  // a group: NV consecutive list entries per warp
     // the last group is filled up with a segment behind the slice, whose bits (the zero words after the bit set)
@@ -942,78 +927,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
         thr_v += 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
     };
-    constexpr int LPT = VEC == 8 ? 4 : 8;  // list entries per thread: 32 elements, one `lost` bit each
-    const bool sparse = n_av <= min(NT * LPT, a.list_cap);
     float xa[NV][VEC], xb[NV][VEC];  // the two groups in flight
     uint32_t ma[NV], mb[NV];
     bool pa = false, pb = false;
-    if (sparse) {
-        // 3a. Few allowed vectors (a grammar mask that admits little): no groups.  The allowed vectors are listed
-        // from the bit set, every thread requests all of its (at most LPT) at once, and after ONE memory round
-        // trip the bound is known and the candidates are appended straight from registers.
-        for (int w = tid; w < a.slice_len / 32; w += NT) {
-            uint32_t t = vector_units(eff[w]);
-            if (!t) continue;
-            uint32_t at = atomicAdd(&sh.n_vl, (uint32_t) __popc(t));
-            for (; t; t &= t - 1u) vlist[at++] = (uint32_t) (w * (32 / VEC) + (__ffs(t) - 1) / VEC);
-        }
-        __syncthreads();
-        const int n_vl = (int) sh.n_vl;  // <= n_av: the history took some out
-        float xv[LPT][VEC];
-        uint32_t mb[LPT];
-        int ev[LPT];
-#pragma unroll
-        for (int u = 0; u < LPT; ++u) {
-            const int j = u * NT + tid;
-            mb[u] = 0u;
-            ev[u] = 0;
-            if (j < n_vl) {
-                ev[u] = (int) vlist[j] * VEC;
-                mb[u] = (eff[ev[u] >> 5] >> (ev[u] & 31)) & kVecBits;
-                load_vec<T, VEC>(x + ev[u], xv[u]);
-            }
-        }
-        float vmx[LPT];
-#pragma unroll
-        for (int u = 0; u < LPT; ++u) {
-            vmx[u] = mb[u] ? vector_max<VEC>(xv[u], mb[u]) : -INFINITY;
-            tmax = fmaxf(tmax, vmx[u]);
-        }
-        done = 1;
-        tighten(tmax);
-        const uint64_t tk0 = (uint64_t) order_word(thr_v) << 32;
-#pragma unroll
-        for (int u = 0; u < LPT; ++u) {
-            if (!(vmx[u] >= thr_v)) continue;
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-                if (((mb[u] >> j) & 1u) && xv[u][j] >= thr_v && xv[u][j] <= FLT_MAX) {
-                    const uint64_t key = make_key(xv[u][j], id0 + (uint32_t) (ev[u] + j));
-                    if (k == 1) best = key > best ? key : best;
-                    else if (key >= tk0 && !push(key, buf, sh, a.cap)) lost |= 1u << (u * VEC + j);
-                }
-            }
-        }
-        if (k > 1 && n_av + VEC > a.trigger) {  // uniform: only then can the buffer fill
-            uint64_t tk = tk0;
-            while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
-                compact<NT>(buf, sel, k, a.cap, sh);
-                if (sh.thr_key > tk) tk = sh.thr_key;
-                uint32_t still = 0u;
-#pragma unroll
-                for (int u = 0; u < LPT; ++u) {
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        if (!((lost >> (u * VEC + j)) & 1u)) continue;
-                        const uint64_t key = make_key(xv[u][j], id0 + (uint32_t) (ev[u] + j));
-                        if (key >= tk && !push(key, buf, sh, a.cap)) still |= 1u << (u * VEC + j);
-                    }
-                }
-                lost = still;
-                if (!__syncthreads_or(lost != 0u)) break;
-            }
-        }
-    } else if constexpr (DIRECT) {
+    if constexpr (DIRECT) {
 #pragma unroll
         for (int i = 0; i < NV; ++i)
 #pragma unroll
@@ -1068,7 +985,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
     }
     FNS_PHASE(9)
-    if (!sparse) tighten(clean_max());
+    tighten(clean_max());
     if (!(tmax >= thr_v)) f0 = f1 = 0ull;  // nothing of this thread can be a candidate: its flags are void
     FNS_PHASE(2)
 
@@ -1078,8 +995,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     // append that finds it full is dropped, and the cursor running past the end afterwards says so.  Only then
     // (many equal values, k near the buffer size) is everything offered again the careful way: every group
     // flagged, the block voting after every round on whether to compact (which also raises the bar) and
-    // repeating the appends that failed.  A sparse slice has appended from registers already and goes the
-    // careful way at once.
+    // repeating the appends that failed.
     uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
     auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add
         v = v > 0.0f ? __fdiv_rn(v, p.repetition) : __fmul_rn(v, p.repetition);
@@ -1099,7 +1015,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
         return -1;
     };
-    for (int attempt = sparse ? 1 : 0; attempt < 2; ++attempt) {
+    for (int attempt = 0; attempt < 2; ++attempt) {
         const bool careful = attempt == 1 && k > 1;
         // (a) the ragged end
         if (rag_key != 0ull) {
@@ -1176,7 +1092,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
         // careful way walks every group instead, one per round, with a vote after each.
         bool listed = true;
-        if (DIRECT && !careful && !sparse) {
+        if (DIRECT && !careful) {
             if constexpr (DIRECT) {
             auto offer_group = [&](int g, float (&xv)[NV][VEC]) {
 #pragma unroll
@@ -1242,7 +1158,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                     else if (key >= thr_key) push(key, buf, sh, a.cap);
                 }
             }
-        } else if (!sparse) {
+        } else {
 #pragma unroll 1
             for (int g = 0; g < n_groups; ++g) {
                 uint32_t bits[NV], lost = 0u;  // lost: elements of this round that found the buffer full
@@ -1558,7 +1474,7 @@ bool make_plan_for(const fns_b200_sampler * s, int dtype, int vocab, int rows, i
     pl.cap = round_up(pl.cap, 2);  // what follows the buffer stays 16-byte aligned
     pl.own_cap = 0;
     if (hist_bound > 0) pl.own_cap = round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4);
-    pl.list_cap = pl.threads * 8;  // the sparse path lists at most 8 vectors per thread
+    pl.list_cap = pl.threads * 8;  // vectors the second pass can take; more than that sends the slice the careful way
     pl.seg_cap = round_up(pl.slice_len / (32 * pl.vec) + 1, 256);  // room for the padding of the last group (<= 256 entries)
     pl.smem_select = (size_t) pl.cap * 8 + (size_t) k_cap * 8 * 4 + (size_t) pl.slice_len / 8 + 32 + (size_t) pl.own_cap * 8 +
                      16 * 16 + (size_t) pl.list_cap * 4 + (size_t) pl.threads * 20 + (size_t) pl.seg_cap * 4 + sizeof(SelectShared) + 16;
