@@ -33,8 +33,8 @@ sys.path.insert(0, ROOT)
 METRIC = "sampler rows/s (V=151936 fp32, mask+penalties+top-k/p, 256 sessions per GPU)"
 WORKLOAD = "sessions256"
 # dram__bytes_read.sum + dram__bytes_write.sum per k_select launch, from the ncu captures summarised under profiles/
-NCU_TRAFFIC_BYTES = 25.4e6
-NCU_TRAFFIC_BYTES_DENSE = 197.6e6
+NCU_TRAFFIC_BYTES = 25.3e6
+NCU_TRAFFIC_BYTES_DENSE = 194.1e6
 
 
 def measured_peaks():
