@@ -24,6 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "-shared",
     "-cudart", "static",
+    "--threads", "3",
 ]
 
 

@@ -8,7 +8,7 @@
 #include <cfloat>
 #include <cstdint>
 
-#include "../../include/fns_b200.h"
+#include "fns_internal.h"
 
 namespace fnsb {
 

@@ -16,7 +16,7 @@
 #include <cstring>
 #include <new>
 
-#include "../../include/fns_b200.h"
+#include "fns_internal.h"
 
 namespace {
 
@@ -255,8 +255,10 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
     }
     if ((err = bring(s.params_h, s.params_d, params_host, (size_t) rows, stable, st)) != cudaSuccess)
         return ecuda(e, err, "params copy");
+    fns_b200_hint_host_logits(e->sampler, in_place != nullptr);
     const int rc = fns_b200_sample_rows(e->sampler, lg, dtype, row_stride, e->vocab, rows, masks_host ? s.masks_d : nullptr,
                                         e->words, hist_d, hstride, hist_len_d, s.params_d, s.tokens_d, st);
+    fns_b200_hint_host_logits(e->sampler, 0);
     if (rc != FNS_B200_OK) return esampler(e, rc);
     if ((err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) !=
             cudaSuccess ||

@@ -40,25 +40,6 @@
 
 namespace fnsb {
 
-#ifdef FNS_PHASE_TIMING  // development aid: block time per phase, summed over blocks (thread 0's clock)
-__device__ unsigned long long g_phase[32];  // [0, 16): sums over blocks; [16, 32): maxima over blocks
-__device__ unsigned g_rowphase[1024][16];   // last launch: cycles per phase of the blocks (blockIdx.y, slice 0)
-#define FNS_PHASE_BEGIN long long ph_t = clock64(); const long long ph_0 = ph_t;
-#define FNS_PHASE(i)                                                           \
-    if (threadIdx.x == 0) {                                                    \
-        const long long ph_n = clock64();                                      \
-        atomicAdd(&g_phase[i], (unsigned long long) (ph_n - ph_t));            \
-        atomicMax(&g_phase[16 + i], (unsigned long long) (ph_n - ph_t));       \
-        atomicMax(&g_phase[16 + 15], (unsigned long long) (ph_n - ph_0));      \
-        if (blockIdx.x == 0 && blockIdx.y < 1024) { g_rowphase[blockIdx.y][i] = (unsigned) (ph_n - ph_t); g_rowphase[blockIdx.y][15] = (unsigned) (ph_n - ph_0); } \
-        ph_t = ph_n;                                                           \
-    }
-#define FNS_MARK(i) __syncthreads(); FNS_PHASE(i)
-#else
-#define FNS_PHASE_BEGIN
-#define FNS_PHASE(i)
-#define FNS_MARK(i)
-#endif
 
 constexpr int kMaxMergeKeys = 8192;   // k_finalize holds the lists of one row in shared memory
 constexpr int kMaxSlices = 128;
@@ -89,6 +70,10 @@ struct SelectArgs {
     int own_cap;     // entries of the list of owned history ids (a multiple of 4), 0: no penalties
     int list_cap;    // entries of the work list of the second pass
     int seg_cap;     // segments of a slice (32 vectors each), a multiple of 4
+    int n_stages;    // k_ring: stages of 8,192 elements that cover the row
+    int ring_depth;  // k_ring: stages of shared memory that the copies rotate through
+    int ring_off;    // k_ring: where the ring starts in the block's shared memory
+    int own_off;     // k_ring: where the list of owned history ids starts
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
     int32_t * out_tokens;       // [rows], may be null
@@ -550,8 +535,12 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
     const uint32_t id0 = (uint32_t) (a.id_base + lo);
+    // Launched with programmatic stream serialisation: this block may start while the previous kernel of the stream
+    // still drains, and the next kernel's blocks may take the places of blocks that have exited (they wait here
+    // too).  Nothing is read from global memory before the previous kernel has finished.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-    FNS_PHASE_BEGIN
     // Everything whose address is known is requested before anything is waited for: the row's parameters, its
     // history length, the first history ids and the mask words.
     const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
@@ -664,7 +653,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     const int n_pen = n_hist + (a.draft ? col : 0);
     uint64_t best = 0ull;      // k == 1: this thread's best key
     __syncthreads();
-    FNS_PHASE(0)
     const int n_seg = (int) sh.n_seg;
     const int n_groups = (n_seg + kWarps * NV - 1) / (kWarps * NV);  // a group: NV consecutive list entries per warp
     // the last group is filled up with a segment behind the slice, whose bits (the zero words after the bit set)
@@ -737,7 +725,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             }
         }
     }
-    FNS_PHASE(12)
     __syncthreads();
     if (use_hist) n_own = (int) sh.n_own;
     // The row's ragged end: the elements of a last, partial vector are taken out of the bit set here, so that the
@@ -754,7 +741,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
         __syncthreads();
     }
-    FNS_PHASE(1)
 
     // 3. Pass 1 over the listed segments: maxima only.  A group gives every warp NV segments, that is every thread
     // NV vectors (16 elements); two groups are in flight (the loads of the next one are issued before the current
@@ -984,10 +970,8 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
             reduce(g + 1, xb, mb, pb);
         }
     }
-    FNS_PHASE(9)
     tighten(clean_max());
     if (!(tmax >= thr_v)) f0 = f1 = 0ull;  // nothing of this thread can be a candidate: its flags are void
-    FNS_PHASE(2)
 
     // 4. The candidates.  Three sources are compared with the final bound and what passes is appended to the
     // buffer: the ragged end, the penalised history ids, and the flagged groups of pass 1 (read again).  With the
@@ -1016,7 +1000,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         return -1;
     };
     for (int attempt = 0; attempt < 2; ++attempt) {
-        const bool careful = attempt == 1 && k > 1;
+        const bool careful = attempt == 1;
         // (a) the ragged end
         if (rag_key != 0ull) {
             if (k == 1) best = rag_key > best ? rag_key : best;
@@ -1076,7 +1060,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                     if (k == 1) best = key > best ? key : best;
                     else if (key >= thr_key) full = !push(key, buf, sh, a.cap);
                 }
-                if (careful && n_own + VEC > a.trigger) {  // uniform: only a long list can fill the buffer
+                if (careful && k > 1 && n_own + VEC > a.trigger) {  // uniform: only a long list can fill the buffer
                     while (__syncthreads_or(full || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
                         compact<NT>(buf, sel, k, a.cap, sh);
                         const uint64_t tk = sh.thr_key;
@@ -1087,7 +1071,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 }
             }
         }
-        FNS_PHASE(6)
         // (c) The flagged groups.  Their vectors go on a work list that the whole block then shares: one vector per
         // thread and round, read again (from L1 / L2, or HBM when a large batch has pushed the row out).  The
         // careful way walks every group instead, one per round, with a vote after each.
@@ -1137,11 +1120,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 }
             }
             __syncthreads();
-            FNS_PHASE(7)
             const int n_work = (int) sh.n_vl;
-#ifdef FNS_PHASE_TIMING
-            if (tid == 0 && blockIdx.x == 0 && blockIdx.y < 1024) { g_rowphase[blockIdx.y][12] = (unsigned) n_work; g_rowphase[blockIdx.y][13] = (unsigned) n_own; g_rowphase[blockIdx.y][14] = sh.n_cand; }
-#endif
             listed = n_work <= a.list_cap;  // uniform; a list that does not fit sends the slice the careful way
 #pragma unroll 1
             for (int i = tid; i < n_work && listed; i += NT) {
@@ -1180,9 +1159,11 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                     for (int j = 0; j < VEC; ++j) {
                         if (!(((bits[i] >> j) & 1u) && xv[i][j] >= thr_v && xv[i][j] <= FLT_MAX)) continue;
                         const uint64_t key = make_key(xv[i][j], id0 + (uint32_t) (e0[i] + j));
-                        if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (i * VEC + j);
+                        if (k == 1) best = key > best ? key : best;
+                        else if (key >= thr_key && !push(key, buf, sh, a.cap)) lost |= 1u << (i * VEC + j);
                     }
                 }
+                if (k == 1) continue;  // greedy: nothing is buffered, so nothing can overflow
                 while (__syncthreads_or(lost != 0u || *(volatile uint32_t *) &sh.n_cand >= (uint32_t) a.trigger)) {
                     compact<NT>(buf, sel, k, a.cap, sh);
                     const uint64_t tk = sh.thr_key;
@@ -1207,10 +1188,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         // The buffer or the work list overflowed: start again from an empty buffer, the careful way.
         __syncthreads();
         if (tid == 0) sh.n_cand = 0u;
+        best = 0ull;
         __syncthreads();
     }
     __syncthreads();
-    FNS_PHASE(3)
 
     // 4. The slice's answer: its best k keys in the total order.  A row that is one slice goes straight on to
     // the draw; otherwise the list goes to global memory and the last block of the row merges.
@@ -1243,9 +1224,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
     } else {
         const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
-#ifdef FNS_PHASE_TIMING
-        if (tid == 0 && blockIdx.x == 0 && blockIdx.y < 1024) g_rowphase[blockIdx.y][11] = (unsigned) n;
-#endif
         uint64_t * dst = whole_row ? sorted : out;
         int got;
         if (n <= kRankSelectMax) {
@@ -1258,13 +1236,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         for (int j = got + tid; j < (whole_row ? a.k_cap : k); j += NT) dst[j] = 0ull;
         if (whole_row) {
             __syncthreads();
-            FNS_PHASE(4)
             draw_tail<NT>(sorted, got, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
-            FNS_PHASE(5)
             return;
         }
     }
-    FNS_PHASE(4)
 
     // 5. The last block of the row to get here merges the slices' lists and draws.  Nobody waits: every block
     // takes a ticket after its list is visible, and the one that draws the last ticket does the work.
@@ -1277,7 +1252,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     }
     __syncthreads();
     if (!sh.is_last) return;
-    FNS_PHASE(6)
     __threadfence();
     const uint64_t * lists = a.cand + (size_t) row * a.slices * a.k_cap;
     if (k == 1) {  // greedy: the largest of the slices' best keys, no sort, no draw
@@ -1300,7 +1274,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         }
         if (oc)
             for (int j = 1 + tid; j < a.k_cap; j += NT) oc[j] = key_to_cand(0ull);
-        FNS_PHASE(5)
         return;
     }
     // the slices' lists, each sorted, side by side in the buffer: [slices][k]
@@ -1309,12 +1282,15 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
         buf[i] = __ldcg(lists + (size_t) l * a.k_cap + j);
     }
     __syncthreads();
-    FNS_PHASE(7)
     const int nk = merge_lists<NT>(buf, a.slices, k, sel, sorted, reinterpret_cast<uint64_t *>(pj), 2 * a.k_cap, sh.sc, k, a.k_cap);
-    FNS_PHASE(10)
     draw_tail<NT>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
-    FNS_PHASE(5)
 }
+
+}  // namespace fnsb
+
+#include "fns_ring.cuh"
+
+namespace fnsb {
 
 // ---- finalize as a kernel of its own -------------------------------------------------------------------------
 constexpr int kFinalThreads = 256;
@@ -1408,6 +1384,7 @@ struct fns_b200_sampler {
     int sm_count;
     int force_slices;
     int force_threads;
+    bool logits_in_host_memory;  // the next call's logits are page-locked host memory (set by the engine glue)
     uint64_t * cand;   // [rows][slices][k_cap] sorted keys of the slices
     size_t cand_entries;
     unsigned * tickets;  // [max_rows], zero between launches
@@ -1424,6 +1401,8 @@ namespace {
 struct Plan {
     int threads, slices, slice_len, cap, trigger, own_cap, vec, list_cap, seg_cap;
     size_t smem_select;
+    bool ring;    // k_ring instead of k_select
+    int n_stages, ring_depth, ring_off, own_off;
 };
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -1481,8 +1460,61 @@ bool make_plan_for(const fns_b200_sampler * s, int dtype, int vocab, int rows, i
     return pl.smem_select <= 200 * 1024;
 }
 
-bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, Plan & pl) {
+// k_ring: one block per row, the row streamed through a ring of shared-memory stages by bulk copies.  Two blocks
+// share an SM when the ring, the bit set and the cell maxima fit twice; a call with no more rows than SMs gives
+// every block an SM of its own and a deeper ring.
+bool make_ring_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, Plan & pl) {
+    const int k_cap = s->k_cap;
+    const size_t esz = dtype == FNS_B200_BF16 ? 2 : 4;
+    pl.ring = true;
+    pl.threads = kRingThreads;
+    pl.slices = 1;
+    pl.slice_len = vocab;
+    pl.vec = (int) (16 / esz);
+    pl.n_stages = (vocab + kStageElems - 1) / kStageElems;
+    if (pl.n_stages > kMaxRingStages) return false;
+    pl.cap = round_up(4 * k_cap > 2048 ? 4 * k_cap : 2048, 2);
+    pl.trigger = pl.cap / 2;
+    pl.own_cap = hist_bound > 0 ? round_up(hist_bound < vocab ? hist_bound : vocab, 4) : 0;
+    pl.list_cap = 4096;
+    pl.seg_cap = 0;
+    const size_t sh_bytes = (sizeof(SelectShared) + 15) & ~(size_t) 15;
+    size_t fixed = 128 + sh_bytes + kMaxRingStages * 4 + (size_t) pl.n_stages * 1024;  // ... | chunk map, stage list | bit set
+    fixed += (size_t) pl.n_stages * 1024;  // cell maxima
+    pl.own_off = (int) fixed;
+    fixed += (size_t) pl.own_cap * 4;
+    pl.ring_off = (int) ((fixed + 127) & ~(size_t) 127);
+    const size_t tail = (size_t) pl.cap * 8 + (size_t) pl.list_cap * 4 + (size_t) k_cap * 8 * 4 + (size_t) pl.own_cap * 4 +
+                        (size_t) kRingThreads * 2 * 8;
+    const size_t stage = (size_t) kStageElems * esz;
+    // an SM has 228 KB of shared memory and every resident block costs 1 KB on top of what it asks for
+    const size_t two_per_sm = 115200, one_per_sm = 225 * 1024;
+    auto depth_for = [&](size_t budget) -> int {
+        if ((size_t) pl.ring_off + tail > budget || (size_t) pl.ring_off + 2 * stage > budget) return 0;
+        const size_t d = (budget - pl.ring_off) / stage;
+        return (int) (d > (size_t) kMaxRingDepth ? kMaxRingDepth : d);
+    };
+    int depth = rows > s->sm_count ? depth_for(two_per_sm) : 0;
+    if (depth < 2) depth = depth_for(one_per_sm);
+    if (depth < 2) return false;
+    if (depth > pl.n_stages) depth = pl.n_stages < 2 ? 2 : pl.n_stages;
+    pl.ring_depth = depth;
+    const size_t ring_bytes = (size_t) depth * stage;
+    pl.smem_select = pl.ring_off + (ring_bytes > tail ? ring_bytes : tail);
+    return true;
+}
+
+// Whole rows (from five rows on) go to k_ring when the call has no mask - every byte of the rows has to move, and
+// the copy engine moves it best - and whenever k_cap exceeds the 512 thread maxima that k_select's bound is made of.
+// Masked calls with k_cap <= 512 stay with k_select: its per-vector skipping and its loads in registers serve a
+// batch better in which a few dense rows stream next to many sparse ones.
+bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, bool masked, Plan & pl) {
     const bool whole_rows = s->force_threads <= 0 && s->force_slices <= 0 && rows > 4;
+    pl.ring = false;
+    if (whole_rows && aligned && !s->logits_in_host_memory && (!masked || s->k_cap > kRingThreads) &&
+        make_ring_plan(s, dtype, vocab, rows, hist_bound, pl))
+        return true;
+    pl.ring = false;
     if (whole_rows && make_plan_for(s, dtype, vocab, rows, hist_bound, aligned, true, pl)) return true;
     return make_plan_for(s, dtype, vocab, rows, hist_bound, aligned, false, pl);  // (a long history may not fit a whole row)
 }
@@ -1502,8 +1534,17 @@ cudaError_t launch_select_d(const SelectArgs & a, int rows, size_t smem, cudaStr
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kern<<<dim3((unsigned) a.slices, (unsigned) rows), NT, smem, st>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned) a.slices, (unsigned) rows);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the prologue overlaps the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 template <typename T, int VEC, int NT>
@@ -1512,6 +1553,7 @@ cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStr
                                                 : launch_select_d<T, VEC, NT, false>(a, rows, smem, st);
 }
 
+#ifndef FNS_DEV_FAST
 template <int NT>
 cudaError_t launch_select_nt(const SelectArgs & a, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
     if (dtype == FNS_B200_BF16)
@@ -1519,10 +1561,40 @@ cudaError_t launch_select_nt(const SelectArgs & a, int dtype, int vec, int rows,
                         : launch_select_t<__nv_bfloat16, 1, NT>(a, rows, smem, st);
     return vec == 4 ? launch_select_t<float, 4, NT>(a, rows, smem, st) : launch_select_t<float, 1, NT>(a, rows, smem, st);
 }
+#endif
 
 cudaError_t launch_select(const SelectArgs & a, int threads, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
+#ifdef FNS_DEV_FAST  // development builds: one instantiation only
+    return launch_select_t<float, 4, 512>(a, rows, smem, st);
+#else
     return threads == 512 ? launch_select_nt<512>(a, dtype, vec, rows, smem, st)
                           : launch_select_nt<256>(a, dtype, vec, rows, smem, st);
+#endif
+}
+
+template <typename T>
+cudaError_t launch_ring_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
+    auto kern = k_ring<T>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned) rows);
+    cfg.blockDim = dim3(kRingThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the prologue overlaps the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
@@ -1573,7 +1645,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     const size_t esz = dtype == FNS_B200_BF16 ? 2 : 4;
     const bool aligned = ((uintptr_t) logits % 16 == 0) && ((size_t) row_stride * esz % 16 == 0 || rows == 1);
     const int hist_bound = (history ? (int) history_stride : 0) + n_draft;
-    if (!make_plan(s, dtype, vocab, rows, hist_bound, aligned, pl)) return fail(s, FNS_B200_ERR_CAPACITY, "no launch plan fits (vocab too large for k_cap)");
+    if (!make_plan(s, dtype, vocab, rows, hist_bound, aligned, masks != nullptr, pl)) return fail(s, FNS_B200_ERR_CAPACITY, "no launch plan fits (vocab too large for k_cap)");
     if ((size_t) rows * pl.slices * s->k_cap > s->cand_entries) return fail(s, FNS_B200_ERR_CAPACITY, "workspace too small for this call");
     SelectArgs a{};
     a.logits = logits;
@@ -1597,6 +1669,10 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.own_cap = pl.own_cap;
     a.list_cap = pl.list_cap;
     a.seg_cap = pl.seg_cap;
+    a.n_stages = pl.n_stages;
+    a.ring_depth = pl.ring_depth;
+    a.ring_off = pl.ring_off;
+    a.own_off = pl.own_off;
     a.cand = s->cand;
     a.tickets = s->tickets;
     a.out_tokens = out_tokens;
@@ -1604,7 +1680,10 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.err = s->err;
     const bool prof = s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size();
     if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3], st);
-    const cudaError_t e = launch_select(a, pl.threads, dtype, pl.vec, rows, pl.smem_select, st);
+    cudaError_t e;
+    if (!pl.ring) e = launch_select(a, pl.threads, dtype, pl.vec, rows, pl.smem_select, st);
+    else if (dtype == FNS_B200_BF16) e = launch_ring_t<__nv_bfloat16>(a, rows, pl.smem_select, st);
+    else e = launch_ring_t<float>(a, rows, pl.smem_select, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "select launch");
     ++s->launches;
     if (prof) {  // the merge and the draw happen inside k_select: the record closes here
@@ -1636,6 +1715,7 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
     s->max_history = max_history;
     s->force_slices = 0;
     s->force_threads = 0;
+    s->logits_in_host_memory = false;
     s->launches = 0;
     s->prof_on = false;
     s->prof_calls = 0;
@@ -1722,8 +1802,14 @@ int fns_b200_device_status(fns_b200_sampler * s, void * stream) {
     if (e != cudaSuccess) return fail_cuda(s, e, "device_status");
     if (flag != 0) {
         cudaMemsetAsync(s->err, 0, sizeof(int), (cudaStream_t) stream);
-        return fail(s, FNS_B200_ERR_DEVICE, flag == 1 ? "candidate buffer overflow" : "history table overflow");
+        return fail(s, FNS_B200_ERR_DEVICE, flag == 3 ? "a bulk copy into shared memory never completed" : "kernel error flag set");
     }
+    return FNS_B200_OK;
+}
+
+int fns_b200_hint_host_logits(fns_b200_sampler * s, int on) {
+    if (!s) return FNS_B200_ERR_ARG;
+    s->logits_in_host_memory = on != 0;
     return FNS_B200_OK;
 }
 
@@ -1743,7 +1829,7 @@ int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, in
                   int * slice_len, int * smem_bytes) {
     if (!s || vocab <= 0 || rows <= 0) return FNS_B200_ERR_ARG;
     Plan pl;
-    if (!make_plan(s, dtype, vocab, rows, history_bound, true, pl)) return FNS_B200_ERR_CAPACITY;
+    if (!make_plan(s, dtype, vocab, rows, history_bound, true, true, pl)) return FNS_B200_ERR_CAPACITY;
     if (slices) *slices = pl.slices;
     if (slice_len) *slice_len = pl.slice_len;
     if (smem_bytes) *smem_bytes = (int) pl.smem_select;
@@ -1836,21 +1922,6 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
     return FNS_B200_OK;
 }
 
-#ifdef FNS_PHASE_TIMING
-// development aid (not part of the ABI header): reads and clears the phase clocks
-int fns_b200_debug_rowphases(unsigned * out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, fnsb::g_rowphase, sizeof(unsigned) * 1024 * 16);
-    return 0;
-}
-int fns_b200_debug_phases(unsigned long long * out8) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out8, fnsb::g_phase, sizeof(unsigned long long) * 32);
-    unsigned long long zero[32] = {};
-    cudaMemcpyToSymbol(fnsb::g_phase, zero, sizeof zero);
-    return 0;
-}
-#endif
 
 int fns_b200_presence_apply(float * x, const float * seen, int n, float penalty, void * stream) {
     if (!x || !seen || n <= 0) return FNS_B200_ERR_ARG;

@@ -57,9 +57,6 @@ SYMBOLS = [
     "fns_b200_presence_apply_col",
     "fns_b200_presence_mark_n",
     "fns_b200_io_advance",
-    "fns_b200_plan",
-    "fns_b200_set_slices",
-    "fns_b200_set_threads",
     "fns_b200_launch_count",
     "fns_b200_profile_begin",
     "fns_b200_profile_end",
@@ -75,6 +72,9 @@ SYMBOLS = [
     "fns_b200_engine_verify",
     "fns_b200_lookup_draft",
 ]
+
+#: exported for the tests, the benchmark and the engine glue only (csrc/fns_internal.h)
+INTERNAL_SYMBOLS = ["fns_b200_plan", "fns_b200_set_slices", "fns_b200_set_threads", "fns_b200_hint_host_logits"]
 
 _lib = None
 
@@ -143,7 +143,8 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_engine_append.argtypes = [vp, vp, i64, i32, vp, vp]
     lib.fns_b200_engine_verify.argtypes = [vp, vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp]
     lib.fns_b200_lookup_draft.argtypes = [vp, i32, i32, vp]
-    for name in SYMBOLS:
+    lib.fns_b200_hint_host_logits.argtypes = [vp, i32]
+    for name in SYMBOLS + INTERNAL_SYMBOLS:
         getattr(lib, name).restype = i32
     lib.fns_b200_last_error.restype = ctypes.c_char_p
     lib.fns_b200_engine_last_error.restype = ctypes.c_char_p

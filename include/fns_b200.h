@@ -241,17 +241,6 @@ int fns_b200_engine_verify(fns_b200_engine * e, const void * logits, int dtype, 
  * occurrence of the final n-gram of the history, n = 4 down to 2.  Returns the number of ids written. */
 int fns_b200_lookup_draft(const int32_t * history_host, int n_history, int want, int32_t * out_host);
 
-/* Launch geometry chosen for a call (slices per row, threads, dynamic shared memory of the select kernel),
- * for benchmarks and tests. */
-int fns_b200_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int history_bound, int * slices,
-                  int * slice_len, int * smem_bytes);
-/* Overrides the number of slices per row (0 = automatic).  For tests that must show that results do not depend
- * on the launch geometry. */
-int fns_b200_set_slices(fns_b200_sampler * s, int slices);
-/* Overrides the block size of the select kernel: 256 (sliced rows), 512 (one block per row when it fits), 0 =
- * automatic.  For the same tests. */
-int fns_b200_set_threads(fns_b200_sampler * s, int threads);
-
 #ifdef __cplusplus
 }
 #endif
