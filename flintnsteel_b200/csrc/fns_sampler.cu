@@ -1523,17 +1523,53 @@ size_t final_smem(int lists, int list_len, int k_cap) {
     return (size_t) lists * list_len * 8 + (size_t) k_cap * 8 * 4 + sizeof(FinalShared) + 16;
 }
 
+// Every kernel that a sampling call can launch opts in to large dynamic shared memory, once per device, before the
+// first launch on it.  Doing all of them together also loads all of them: with lazy module loading the first use
+// of a kernel allocates device memory, which must not happen later (inside a stream capture, or in a process
+// whose arena has taken the whole device).
+template <typename K>
+cudaError_t opt_in(K kern, int bytes) { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); }
+
+template <typename T, int VEC>
+cudaError_t opt_in_select() {
+    cudaError_t e = opt_in(k_select<T, VEC, 512, false>, 200 * 1024);
+    if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 512, true>, 200 * 1024);
+#ifndef FNS_DEV_FAST
+    if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 256, false>, 200 * 1024);
+    if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 256, true>, 200 * 1024);
+#endif
+    return e;
+}
+
+cudaError_t configure_kernels_once() {  // call with the device current
+    static std::mutex lock;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> hold(lock);
+    if (configured[dev]) return cudaSuccess;
+    e = opt_in_select<float, 4>();
+#ifndef FNS_DEV_FAST
+    if (e == cudaSuccess) e = opt_in_select<float, 1>();
+    if (e == cudaSuccess) e = opt_in_select<__nv_bfloat16, 8>();
+    if (e == cudaSuccess) e = opt_in_select<__nv_bfloat16, 1>();
+#endif
+    if (e == cudaSuccess) e = opt_in(k_ring<float>, 226 * 1024);
+    if (e == cudaSuccess) e = opt_in(k_ring<__nv_bfloat16>, 226 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_ring<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_ring<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = opt_in(k_finalize, 200 * 1024);
+    if (e == cudaSuccess) configured[dev] = true;
+    return e;
+}
+
 template <typename T, int VEC, int NT, bool DIRECT>
 cudaError_t launch_select_d(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
     auto kern = k_select<T, VEC, NT, DIRECT>;
-    static bool configured[64] = {};  // per device: the opt-in to large dynamic shared memory is sticky
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
+    const cudaError_t ce = configure_kernels_once();
+    if (ce != cudaSuccess) return ce;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned) a.slices, (unsigned) rows);
     cfg.blockDim = dim3(NT);
@@ -1575,15 +1611,8 @@ cudaError_t launch_select(const SelectArgs & a, int threads, int dtype, int vec,
 template <typename T>
 cudaError_t launch_ring_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
     auto kern = k_ring<T>;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
+    const cudaError_t ce = configure_kernels_once();
+    if (ce != cudaSuccess) return ce;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned) rows);
     cfg.blockDim = dim3(kRingThreads);
@@ -1599,14 +1628,8 @@ cudaError_t launch_ring_t(const SelectArgs & a, int rows, size_t smem, cudaStrea
 
 cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
     const size_t smem = final_smem(a.lists, a.list_len, a.k_cap);
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(k_finalize, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
+    const cudaError_t ce = configure_kernels_once();
+    if (ce != cudaSuccess) return ce;
     k_finalize<<<(unsigned) rows, kFinalThreads, smem, st>>>(a);
     return cudaGetLastError();
 }
@@ -1726,6 +1749,10 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
         return FNS_B200_ERR_CUDA;
     }
     s->sm_count = prop.multiProcessorCount;
+    if (configure_kernels_once() != cudaSuccess) {
+        delete s;
+        return FNS_B200_ERR_CUDA;
+    }
     // Candidate workspace: the largest rows * slices any plan can produce, bounded by the merge limit.
     int max_slices = kMaxMergeKeys / k_cap;
     if (max_slices > kMaxSlices) max_slices = kMaxSlices;
@@ -1997,8 +2024,12 @@ extern "C" int fns_b200_sample_rows_noalloc(int device, const void * logits, int
         std::lock_guard<std::mutex> hold(g_noalloc_lock);
         if (!g_noalloc_ptr[device]) {
             void * p = nullptr;
-            const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
             if (e != cudaSuccess || !p) return fail_text(FNS_B200_ERR_CUDA, cudaGetErrorString(e));
+            // every kernel this entry point can ever launch is loaded and configured now, whatever the shape of
+            // this first call: later calls of other shapes (other dtype, row count or alignment) find nothing to set up
+            e = configure_kernels_once();
+            if (e != cudaSuccess) return fail_text(FNS_B200_ERR_CUDA, cudaGetErrorString(e));
             g_noalloc_ptr[device] = static_cast<unsigned char *>(p);
         }
         base = g_noalloc_ptr[device];

@@ -81,3 +81,20 @@ def test_make_params_defaults_are_the_references():
     p = sampler.make_params(3)
     assert np.all(p["temperature"] == 0) and np.all(p["top_p"] == 1) and np.all(p["top_k"] == 0)
     assert np.all(p["repetition"] == 1) and np.all(p["presence"] == 0) and np.all(p["min_p"] == 0)
+
+
+def test_lookup_draft_of_the_library_matches_the_oracle(library_path, oracle):
+    """fns_b200_lookup_draft (include/fns/lookup.h:12-27) is host code: the reference's cases and 1,000 random
+    histories through the library's own entry point, against the oracle's restatement."""
+    h = [1, 2, 3, 4, 9, 9, 1, 2, 3, 4]
+    assert list(sampler.lookup_draft(h, 3)) == [9, 9, 1]
+    assert list(sampler.lookup_draft([7, 8, 5, 7, 8], 4)) == [5, 7, 8]
+    assert list(sampler.lookup_draft([1, 2, 3], 2)) == []
+    assert list(sampler.lookup_draft([1, 1, 1, 1, 1, 1], 2)) == [1]
+    assert list(sampler.lookup_draft([], 2)) == [] and list(sampler.lookup_draft([5, 5, 5], 0)) == []
+    g = np.random.default_rng(12)
+    for _ in range(1000):
+        n = int(g.integers(0, 60))
+        hist = g.integers(0, int(g.integers(2, 7)), size=n).astype(np.int32)  # a small alphabet: n-grams repeat
+        want = int(g.integers(1, 9))
+        assert list(sampler.lookup_draft(hist, want)) == list(oracle.lookup_draft(hist, want)), (hist.tolist(), want)

@@ -112,3 +112,52 @@ def test_verify_window_matches_the_oracle(dev, oracle):
     for i in range(16):
         et, ea = oracle.verify_window(sw.logits[i * (n_draft + 1):(i + 1) * (n_draft + 1)], sw.draft[i], sw.params[i:i + 1])
         assert accept[i] == ea and np.array_equal(tokens[i], et), f"window {i}"
+
+
+def test_verify_with_masks_and_device_side_history(dev, oracle):
+    """Engine::verify with per-column masks (src/engine.cu:734-744) after the sessions' histories were filled by
+    engine_append: column c is penalised with the session history plus draft[0 .. c) (src/kernels.cu:738-741)."""
+    windows, n_draft, vocab, steps = 5, 3, 20_000, 9
+    W = n_draft + 1
+    sw = wl.spec_windows(seed=14, windows=windows, n_draft=n_draft, vocab=vocab, temperature=0.8)
+    sw.params["presence"] = 0.9
+    sw.params["top_k"] = 24
+    g = wl.rng(15)
+    masks = np.stack([wl.random_mask(g, vocab, 0.4) for _ in range(windows * W)])
+    eng = Engine(0, max_rows=windows * W, vocab=vocab, k_cap=64, max_history=steps + 4)
+    eng.reset()
+    # nine committed tokens per session (presence_commit): device-side histories, one column at a time
+    committed = g.integers(0, vocab, size=(windows, steps), dtype=np.int32)
+    committed[2, 3] = -1  # "no token" is skipped (src/kernels.cu:730)
+    for t in range(steps):
+        col = torch.from_numpy(np.ascontiguousarray(committed[:, t])).to(dev)
+        eng.append(col.data_ptr(), 1, windows)
+    torch.cuda.synchronize()
+    tokens, accept = eng.verify(torch.from_numpy(sw.logits).to(dev), sw.draft, sw.params, masks_host=masks)
+    eng.close()
+    for i in range(windows):
+        hist = committed[i][committed[i] >= 0]
+        et, ea = oracle.verify_window(sw.logits[i * W:(i + 1) * W], sw.draft[i], sw.params[i:i + 1],
+                                      masks=masks[i * W:(i + 1) * W], hist=hist)
+        assert accept[i] == ea and np.array_equal(tokens[i], et), f"window {i}"
+
+
+def test_compat_shim_grows_its_workspace(dev, library_path):
+    """fns::k::argmax on a vocabulary larger than the shim's default workspace (262,144): the per-device handle is
+    replaced by a larger one and the next, smaller call still works."""
+    import ctypes
+
+    lib = ctypes.CDLL(library_path)
+    argmax = lib._ZN3fns1k6argmaxEPKfiPiP11CUstream_stPKj
+    argmax.argtypes, argmax.restype = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p], None
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    out = torch.zeros(3, dtype=torch.int32, device=dev)
+    small = torch.zeros(1000, device=dev)
+    small[123] = 1.0
+    big = torch.zeros(300_001, device=dev)
+    big[299_999] = 2.0
+    argmax(small.data_ptr(), 1000, out[0:1].data_ptr(), st, None)
+    argmax(big.data_ptr(), 300_001, out[1:2].data_ptr(), st, None)
+    argmax(small.data_ptr(), 1000, out[2:3].data_ptr(), st, None)
+    torch.cuda.synchronize()
+    assert out.tolist() == [123, 299_999, 123]
