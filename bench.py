@@ -111,10 +111,6 @@ def run_b200(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # stdout carries ONE JSON line: NCCL's banner and anything else a library prints go to stderr
-        if "FNS_NCCL_DEBUG" in os.environ:
-            os.environ["NCCL_DEBUG"] = os.environ["FNS_NCCL_DEBUG"]
-        else:
-            os.environ.pop("NCCL_DEBUG", None)
         sys.stdout.flush()
         json_fd = os.dup(1)
         os.dup2(2, 1)
@@ -400,15 +396,15 @@ def reference_gpu(torch, dev, w, d):
 
 
 def vocab_sharded(torch, dist, dev, local, rank, world):
-    """64 rows x V = 262,144 bf16 split evenly by vocabulary: per-shard top-1024, one NCCL all-gather of
-    (value, id) candidates, merge + draw on every rank."""
+    """64 rows x V = 262,144 bf16 split evenly by vocabulary through the C++ dispatcher (fns_b200_mg_*): per-shard
+    top-1024, one NCCL all-gather of (value, id) candidates, merge + draw on every rank.  The three steps are timed
+    with CUDA events inside the library; rank 0's tokens are compared with the unsharded path on the same rows."""
     from flintnsteel_b200 import workloads as wl
     from flintnsteel_b200.dispatch import VocabSharded
     from flintnsteel_b200.sampler import Sampler, params_to_device
 
     w = wl.large_vocab(seed=0, rows=64)
-    s = Sampler(local, max_rows=w.rows, max_vocab=w.vocab, k_cap=1024, max_history=0)
-    vs = VocabSharded(s, w.vocab, 1024, rank, world)
+    vs = VocabSharded(local, w.vocab, 1024, rank, world, max_rows=w.rows)
     lo, hi = vs.lo, vs.hi
     lg = torch.from_numpy(np.ascontiguousarray(w.logits[:, lo:hi]).view(np.int16)).to(dev).view(torch.bfloat16)
     masks = torch.from_numpy(np.ascontiguousarray(w.masks[:, lo // 32:(hi + 31) // 32]).view(np.int32)).to(dev)
@@ -427,14 +423,32 @@ def vocab_sharded(torch, dist, dev, local, rank, world):
     torch.cuda.synchronize()
     t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    vs.profile_begin(steps)
+    for _ in range(steps):
+        vs.sample(lg, pd, out, masks_shard=masks)
+    sel_us, exch_us, fin_us, _ = vs.profile_end()
+    stage = torch.tensor([sel_us, exch_us, fin_us], dtype=torch.float64, device=dev)
+    dist.all_reduce(stage, op=dist.ReduceOp.MAX)
     same = out.clone()
     dist.broadcast(same, 0)
-    agree = bool(torch.equal(same, out))
-    flag = torch.tensor([1 if agree else 0], device=dev)
+    flag = torch.tensor([1 if torch.equal(same, out) else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    matches = None
+    if rank == 0:  # the whole rows on one GPU, no exchange: a product-vs-product check that can fail
+        s = Sampler(local, max_rows=w.rows, max_vocab=w.vocab, k_cap=1024, max_history=0)
+        full = torch.from_numpy(w.logits.view(np.int16)).to(dev).view(torch.bfloat16)
+        fm = torch.from_numpy(w.masks.view(np.int32)).to(dev)
+        direct = torch.empty(w.rows, dtype=torch.int32, device=dev)
+        s.sample_rows(full, pd, direct, masks=fm)
+        torch.cuda.synchronize()
+        matches = bool(torch.equal(direct, out))
+        s.close()
+    vs.close()
     ms = float(t.item()) / steps
     return {"rows_per_s": w.rows / (ms / 1e3), "ms_per_step": ms, "rows": w.rows, "vocab": w.vocab, "k": 1024,
             "allgather_bytes_per_rank": w.rows * 1024 * 8, "all_ranks_agree": bool(flag.item()),
+            "matches_unsharded": matches, "select_us": float(stage[0]), "allgather_us": float(stage[1]),
+            "finalize_us": float(stage[2]), "stage_note": "CUDA events inside the library, max over ranks",
             "scaling": "strong (the vocabulary is split)"}
 
 

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfns_b200.so")
-SOURCES = ["fns_sampler.cu", "fns_compat.cu", "fns_engine.cu"]
+SOURCES = ["fns_sampler.cu", "fns_compat.cu", "fns_engine.cu", "fns_mg.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17",
@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "-shared",
     "-cudart", "static",
-    "--threads", "3",
+    "--threads", "4",
 ]
 
 
@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(HERE, "..", "include"), "-o", LIB_PATH, *sources()]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(HERE, "..", "include"), "-o", LIB_PATH, *sources(), "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -1,30 +1,34 @@
-"""Multi-GPU dispatcher: one process per GPU, ``torch.distributed`` for the plumbing.
+"""Multi-GPU dispatcher: one process per GPU.  A thin ctypes layer over ``fns_b200_mg_*`` (csrc/fns_mg.cu); the
+partitioning, the exchange and the launch order live in the C++ library, so a C++ engine calls the same code.
 
 The reference is single-GPU, one row per call (its docs/ENGINE.md:132); this layer is new.  Two partitions:
 
-* ``RowSharded``   - independent sessions.  Rows [lo, hi) of the batch live on this rank; every rank samples its
-                     own rows with its own workspace and stream.  No collective on the data path (tokens can be
-                     gathered afterwards: 4 bytes per row).
-* ``VocabSharded`` - one very large vocabulary split evenly over the ranks.  Each rank selects the top-k_cap
-                     (value, id) candidates of its shard of every row, the lists are exchanged with ONE
-                     all-gather (k_cap * 8 bytes per row per rank) into local memory, and every rank runs the
-                     same merge + draw on the gathered lists, so all ranks hold the same tokens without a
-                     broadcast.  Exact for the same reason the reference's 128 slices are
-                     (src/kernels.cu:594-597): the global top-k is contained in the union of the shards' top-k,
-                     and the merge orders by (value, id) alone, so the result does not depend on the number of
-                     shards.
+* ``RowSharded``   - independent sessions.  Every rank samples the rows its own LM head produced, with its own
+                     workspace and stream.  No collective on the data path (tokens can be gathered afterwards:
+                     4 bytes per row).
+* ``VocabSharded`` - one very large vocabulary split evenly over the ranks on 32-id boundaries.  Each rank selects
+                     the top-k_cap (value, id) candidates of its shard of every row, ONE NCCL all-gather brings
+                     the lists into local memory (k_cap * 8 bytes per row and rank), and every rank runs the same
+                     merge + draw, so all ranks hold the same tokens without a broadcast.  Exact for the reason the
+                     reference's 128 slices are (src/kernels.cu:594-597).
 
-The kernels come from ``backend`` (a ``flintnsteel_b200.sampler.Sampler``); the dispatcher only allocates
-tensors and calls the collective.
+``torch.distributed`` is used for one thing only: to hand rank 0's NCCL unique id to the other ranks when the
+dispatcher is created.  The library then owns its communicator.
 """
 from __future__ import annotations
 
-import torch
-import torch.distributed as dist
+import ctypes
+
+import numpy as np
+
+from . import sampler as _s
+
+ROWS, VOCAB = 0, 1
+ID_BYTES = 128
 
 
 def shard_range(total: int, rank: int, world: int) -> tuple[int, int]:
-    """Contiguous near-even split: the first ``total % world`` ranks get one more."""
+    """Contiguous near-even split: the first ``total % world`` ranks get one more (the rule of fns_b200_mg_range)."""
     base, extra = divmod(total, world)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
@@ -37,64 +41,122 @@ def vocab_shard(vocab: int, rank: int, world: int) -> tuple[int, int]:
     return wlo * 32, min(vocab, whi * 32)
 
 
-class RowSharded:
+def _exchange_unique_id(rank: int, world: int, group=None) -> bytes:
+    """Rank 0 asks NCCL for a unique id; every rank gets the same 128 bytes (through the caller's process group)."""
+    import torch
+    import torch.distributed as dist
+
+    lib = _s.load_library()
+    buf = (ctypes.c_ubyte * ID_BYTES)()
+    if rank == 0:
+        rc = lib.fns_b200_mg_unique_id(buf)
+        if rc != _s.OK:
+            raise _s.SamplerError(rc, "fns_b200_mg_unique_id failed (libnccl.so.2 not loadable?)")
+    t = torch.tensor(list(buf), dtype=torch.uint8)
+    if dist.get_backend(group) == "nccl":
+        t = t.cuda()
+    dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    return bytes(t.cpu().tolist())
+
+
+class _Dispatcher:
+    mode = ROWS
+
+    def __init__(self, device: int, vocab: int, k_cap: int, rank: int = 0, world: int = 1, max_rows: int = 256,
+                 max_history: int = 0, group=None, ops=None):
+        self.lib = _s.load_library()
+        self.device, self.vocab, self.k_cap, self.rank, self.world = device, vocab, k_cap, rank, world
+        h = ctypes.c_void_p()
+        self._host_only = ops is not None
+        if ops is not None:  # a table of stand-ins (tests): no GPU, no NCCL
+            self._ops = ops
+            rc = self.lib.fns_b200_mg_create_with_ops(rank, world, self.mode, max_rows, vocab, k_cap, max_history,
+                                                      ctypes.addressof(ops), ctypes.byref(h))
+        else:
+            uid = _exchange_unique_id(rank, world, group) if world > 1 else None
+            rc = self.lib.fns_b200_mg_create(device, rank, world, self.mode, max_rows, vocab, k_cap, max_history, uid,
+                                             None, ctypes.byref(h))
+        if rc != _s.OK:
+            raise _s.SamplerError(rc, "fns_b200_mg_create failed")
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.fns_b200_mg_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != _s.OK:
+            raise _s.SamplerError(rc, self.lib.fns_b200_mg_last_error(self.handle).decode())
+
+    def range(self, total_rows: int = 0) -> tuple[int, int]:
+        lo, hi = ctypes.c_int(), ctypes.c_int()
+        self._check(self.lib.fns_b200_mg_range(self.handle, total_rows, ctypes.byref(lo), ctypes.byref(hi)))
+        return lo.value, hi.value
+
+    def _stream(self, stream):
+        if stream is not None:
+            return stream
+        return None if self._host_only else _s._stream()
+
+    def _sample(self, logits, params, out, masks, history, history_len, stream):
+        self._check(self.lib.fns_b200_mg_sample_rows(
+            self.handle, _s._ptr(logits), _s._dtype_code(logits), logits.stride(0), logits.shape[0],
+            _s._ptr(masks), masks.stride(0) if masks is not None else 0,
+            _s._ptr(history), history.stride(0) if history is not None else 0, _s._ptr(history_len),
+            _s._ptr(params), _s._ptr(out), stream))
+        return out
+
+    def profile_begin(self, max_calls: int):
+        self._check(self.lib.fns_b200_mg_profile_begin(self.handle, max_calls))
+
+    def profile_end(self):
+        """(select_us, exchange_us, finalize_us, calls): device time per call of the three steps."""
+        a, b, c, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_double(), ctypes.c_int()
+        self._check(self.lib.fns_b200_mg_profile_end(self.handle, _s._stream(), ctypes.byref(a), ctypes.byref(b),
+                                                     ctypes.byref(c), ctypes.byref(n)))
+        return a.value, b.value, c.value, n.value
+
+
+class RowSharded(_Dispatcher):
     """Independent sessions: this rank owns rows ``shard_range(total_rows, rank, world)``."""
 
-    def __init__(self, backend, rank: int = 0, world: int = 1, group=None):
-        self.backend, self.rank, self.world, self.group = backend, rank, world, group
+    mode = ROWS
 
     def rows(self, total_rows: int) -> tuple[int, int]:
-        return shard_range(total_rows, self.rank, self.world)
+        return self.range(total_rows)
 
-    def sample(self, logits, params, out, masks=None, history=None, history_len=None):
+    def sample(self, logits, params, out, masks=None, history=None, history_len=None, stream=None):
         """``logits`` etc. hold THIS rank's rows only (the LM head that produced them ran here)."""
-        return self.backend.sample_rows(logits, params, out, masks=masks, history=history, history_len=history_len)
+        return self._sample(logits, params, out, masks, history, history_len, self._stream(stream))
 
-    def gather_tokens(self, local_tokens, total_rows: int):
-        """Optional: every rank receives all tokens, in row order.  Shards of unequal size are padded to the
-        largest for the collective (equal contributions on every backend) and trimmed afterwards."""
-        if self.world == 1:
-            return local_tokens
-        sizes = [hi - lo for lo, hi in (shard_range(total_rows, r, self.world) for r in range(self.world))]
-        width = max(sizes)
-        padded = torch.full((width,), -1, dtype=local_tokens.dtype, device=local_tokens.device)
-        padded[: local_tokens.numel()] = local_tokens
-        out = torch.empty(self.world * width, dtype=local_tokens.dtype, device=local_tokens.device)
-        dist.all_gather_into_tensor(out, padded, group=self.group)
-        if all(n == width for n in sizes):
-            return out
-        return torch.cat([out[r * width: r * width + n] for r, n in enumerate(sizes)])
+    def gather_tokens(self, local_tokens, total_rows: int, out=None, stream=None):
+        """Optional: every rank receives all tokens, in row order."""
+        import torch
+
+        if out is None:
+            out = torch.empty(total_rows, dtype=torch.int32, device=local_tokens.device)
+        self._check(self.lib.fns_b200_mg_gather_tokens(self.handle, _s._ptr(local_tokens), total_rows, _s._ptr(out),
+                                                       self._stream(stream)))
+        return out
 
 
-class VocabSharded:
-    """One vocabulary over ``world`` ranks; this rank owns ids ``vocab_shard(vocab, rank, world)``."""
+class VocabSharded(_Dispatcher):
+    """One vocabulary over ``world`` ranks; this rank owns ids ``[self.lo, self.hi)``."""
 
-    def __init__(self, backend, vocab: int, k_cap: int, rank: int = 0, world: int = 1, group=None):
-        self.backend, self.vocab, self.k_cap = backend, vocab, k_cap
-        self.rank, self.world, self.group = rank, world, group
-        self.lo, self.hi = vocab_shard(vocab, rank, world)
-        self._local = None
-        self._gathered = None
+    mode = VOCAB
 
-    def _buffers(self, rows: int, device):
-        if self._local is None or self._local.shape[0] != rows or self._local.device != device:
-            self._local = torch.empty((rows, self.k_cap, 2), dtype=torch.int32, device=device)
-            self._gathered = torch.empty((self.world, rows, self.k_cap, 2), dtype=torch.int32, device=device)
-        return self._local, self._gathered
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.lo, self.hi = self.range()
 
-    def sample(self, logits_shard, params, out, masks_shard=None, history=None, history_len=None):
+    def sample(self, logits_shard, params, out, masks_shard=None, history=None, history_len=None, stream=None):
         """``logits_shard``: [rows][hi - lo] of this rank's ids; ``masks_shard``: the matching words
         [rows][(hi - lo + 31) // 32]; ``history`` holds GLOBAL ids; ``out``: int32 [rows], the same on every rank."""
-        rows = logits_shard.shape[0]
-        local, gathered = self._buffers(rows, logits_shard.device)
-        self.backend.select_rows(logits_shard, params, local, id_base=self.lo, masks=masks_shard, history=history,
-                                 history_len=history_len, vocab=self.hi - self.lo)
-        if self.world > 1:
-            # the output is the ranks' [rows][k_cap] blocks one after the other (dim 0 concatenation)
-            dist.all_gather_into_tensor(gathered.view(self.world * rows, self.k_cap, 2), local, group=self.group)
-        else:
-            gathered = local[None]
-        # gathered is [world][rows][k_cap]: list l of row r starts at l * rows * k_cap + r * k_cap
-        self.backend.finalize_rows(gathered, self.world, self.k_cap, rows, params, out_tokens=out,
-                                   list_stride=rows * self.k_cap, row_stride=self.k_cap)
-        return out
+        return self._sample(logits_shard, params, out, masks_shard, history, history_len, self._stream(stream))

@@ -71,10 +71,20 @@ SYMBOLS = [
     "fns_b200_engine_append",
     "fns_b200_engine_verify",
     "fns_b200_lookup_draft",
+    "fns_b200_mg_unique_id",
+    "fns_b200_mg_create",
+    "fns_b200_mg_destroy",
+    "fns_b200_mg_last_error",
+    "fns_b200_mg_range",
+    "fns_b200_mg_sample_rows",
+    "fns_b200_mg_gather_tokens",
+    "fns_b200_mg_profile_begin",
+    "fns_b200_mg_profile_end",
 ]
 
 #: exported for the tests, the benchmark and the engine glue only (csrc/fns_internal.h)
-INTERNAL_SYMBOLS = ["fns_b200_plan", "fns_b200_set_slices", "fns_b200_set_threads", "fns_b200_hint_host_logits"]
+INTERNAL_SYMBOLS = ["fns_b200_plan", "fns_b200_set_slices", "fns_b200_set_threads", "fns_b200_hint_host_logits",
+                    "fns_b200_mg_create_with_ops"]
 
 _lib = None
 
@@ -107,6 +117,7 @@ def load_library() -> ctypes.CDLL:
         )
     lib = ctypes.CDLL(path)
     vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+    f64p = ctypes.POINTER(ctypes.c_double)
     lib.fns_b200_create.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(vp)]
     lib.fns_b200_destroy.argtypes = [vp]
     lib.fns_b200_last_error.argtypes = [vp]
@@ -128,7 +139,6 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_plan.argtypes = [vp, i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.fns_b200_set_slices.argtypes = [vp, i32]
     lib.fns_b200_set_threads.argtypes = [vp, i32]
-    f64p = ctypes.POINTER(ctypes.c_double)
     lib.fns_b200_launch_count.argtypes = [vp]
     lib.fns_b200_profile_begin.argtypes = [vp, i32]
     lib.fns_b200_profile_end.argtypes = [vp, vp, f64p, f64p, ctypes.POINTER(i32)]
@@ -144,10 +154,21 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_engine_verify.argtypes = [vp, vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp]
     lib.fns_b200_lookup_draft.argtypes = [vp, i32, i32, vp]
     lib.fns_b200_hint_host_logits.argtypes = [vp, i32]
+    lib.fns_b200_mg_unique_id.argtypes = [vp]
+    lib.fns_b200_mg_create.argtypes = [i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, ctypes.POINTER(vp)]
+    lib.fns_b200_mg_create_with_ops.argtypes = [i32, i32, i32, i32, i32, i32, i32, vp, ctypes.POINTER(vp)]
+    lib.fns_b200_mg_destroy.argtypes = [vp]
+    lib.fns_b200_mg_last_error.argtypes = [vp]
+    lib.fns_b200_mg_range.argtypes = [vp, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.fns_b200_mg_sample_rows.argtypes = [vp, vp, i32, i64, i32, vp, i64, vp, i64, vp, vp, vp, vp]
+    lib.fns_b200_mg_gather_tokens.argtypes = [vp, vp, i32, vp, vp]
+    lib.fns_b200_mg_profile_begin.argtypes = [vp, i32]
+    lib.fns_b200_mg_profile_end.argtypes = [vp, vp, f64p, f64p, f64p, ctypes.POINTER(i32)]
     for name in SYMBOLS + INTERNAL_SYMBOLS:
         getattr(lib, name).restype = i32
     lib.fns_b200_last_error.restype = ctypes.c_char_p
     lib.fns_b200_engine_last_error.restype = ctypes.c_char_p
+    lib.fns_b200_mg_last_error.restype = ctypes.c_char_p
     lib.fns_b200_launch_count.restype = ctypes.c_int64
     lib.fns_b200_engine_sampler.restype = vp
     lib.fns_b200_engine_device_tokens.restype = vp

@@ -79,8 +79,8 @@ int fns_b200_destroy(fns_b200_sampler * s);
 /* Text of the last failure on this handle (host string, valid until the next call on the handle). */
 const char * fns_b200_last_error(const fns_b200_sampler * s);
 /* Synchronises the stream and returns FNS_B200_ERR_DEVICE if a kernel of this handle recorded an internal
- * error since the last call (candidate buffer or history table overflow; neither can happen within the
- * limits checked at launch).  For tests; the sampling calls themselves never synchronise. */
+ * error since the last call: a bulk copy into shared memory that did not complete within the kernel's bounded wait
+ * (the rows of that call are then not valid).  For tests; the sampling calls themselves never synchronise. */
 int fns_b200_device_status(fns_b200_sampler * s, void * stream);
 int fns_b200_k_cap(const fns_b200_sampler * s);
 
@@ -120,8 +120,9 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
  * Limits: rows <= 64 per call, k_cap fixed at 64 (params.top_k <= 0 or > 64 means 64); larger calls are refused
  * with FNS_B200_ERR_CAPACITY and a text in error_text (may be NULL).  All other arguments as
  * fns_b200_sample_rows; `device` is the GPU that owns the buffers.
- * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device): make
- * that first call before starting any stream capture.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device) and loads
+ * and configures every kernel the entry point can launch, whatever the shape of that first call: make it before
+ * starting any stream capture; later calls of any shape set nothing up.
  * All calls on a GPU share the one array, which keeps the previous call's contents (this call clears what has to
  * start at zero): calls that overlap on the GPU, on any streams, race with each other; issue them on one stream
  * or order them with events. */
@@ -240,6 +241,49 @@ int fns_b200_engine_verify(fns_b200_engine * e, const void * logits, int dtype, 
 /* Prompt-lookup draft (include/fns/lookup.h:12-27) on the host: the continuation of the latest earlier
  * occurrence of the final n-gram of the history, n = 4 down to 2.  Returns the number of ids written. */
 int fns_b200_lookup_draft(const int32_t * history_host, int n_history, int want, int32_t * out_host);
+
+/* ---- multi-GPU dispatcher ---------------------------------------------------------------------------------------
+ * No counterpart in the reference, which is single-GPU and samples one row per call (docs/ENGINE.md:132).  One
+ * process per GPU; every rank creates a dispatcher with its own rank.  Two partitions of the sampler's work:
+ *   FNS_B200_MG_ROWS   independent sessions: every rank samples the rows its own LM head produced; no collective
+ *                      on the data path (fns_b200_mg_gather_tokens collects the tokens afterwards if wanted)
+ *   FNS_B200_MG_VOCAB  one large vocabulary split evenly on 32-id boundaries: per-shard top-k_cap
+ *                      (fns_b200_select_rows), ONE NCCL all-gather of the (value, id) lists over NVLink
+ *                      (k_cap * 8 bytes per row and rank), then the merge + draw (fns_b200_finalize_rows) on every
+ *                      rank, so every rank ends with the same tokens.  The result does not depend on the number of
+ *                      shards: the global top-k lies in the union of the shards' top-k (the reference's argument
+ *                      for its 128 slices, src/kernels.cu:594-597) and the merge orders by (value, id) alone.
+ * All three steps are enqueued on the caller's stream with no host work in between.  NCCL is loaded at run time
+ * (libnccl.so.2) and only when world > 1. */
+typedef struct fns_b200_mg fns_b200_mg;
+enum { FNS_B200_MG_ROWS = 0, FNS_B200_MG_VOCAB = 1 };
+#define FNS_B200_MG_ID_BYTES 128
+/* ncclGetUniqueId: rank 0 calls it and hands the 128 bytes to every rank (by whatever channel the host has). */
+int fns_b200_mg_unique_id(void * id_host);
+/* Collective over the ranks when world > 1 (ncclCommInitRank) unless nccl_comm, an existing ncclComm_t of the same
+ * ranks, is given (then unique_id_host may be NULL; the communicator stays the caller's).  vocab is the FULL
+ * vocabulary in both modes; in VOCAB mode k_cap * world <= 8192. */
+int fns_b200_mg_create(int device, int rank, int world, int mode, int max_rows, int vocab, int k_cap, int max_history,
+                       const void * unique_id_host, void * nccl_comm, fns_b200_mg ** out);
+int fns_b200_mg_destroy(fns_b200_mg * m);
+const char * fns_b200_mg_last_error(const fns_b200_mg * m);
+/* What this rank owns: ROWS: rows [lo, hi) of a batch of total_rows; VOCAB: token ids [lo, hi) (lo a multiple of 32). */
+int fns_b200_mg_range(const fns_b200_mg * m, int total_rows, int * lo, int * hi);
+/* ROWS: as fns_b200_sample_rows on this rank's rows.  VOCAB: logits are [rows][row_stride] holding this rank's ids
+ * [lo, hi) of every row, masks the matching words [rows][mask_stride_words] (word 0 = ids lo .. lo + 31), history
+ * GLOBAL ids; out_tokens [rows] is the same on every rank.  Every rank must make the same sequence of calls. */
+int fns_b200_mg_sample_rows(fns_b200_mg * m, const void * logits, int dtype, int64_t row_stride, int rows,
+                            const uint32_t * masks, int64_t mask_stride_words, const int32_t * history,
+                            int64_t history_stride, const int32_t * history_len, const fns_b200_params * params,
+                            int32_t * out_tokens, void * stream);
+/* ROWS: every rank receives the tokens of all total_rows rows in row order (one all-gather of 4 bytes per row). */
+int fns_b200_mg_gather_tokens(fns_b200_mg * m, const int32_t * local_tokens, int total_rows, int32_t * all_tokens,
+                              void * stream);
+/* Device time of the three steps for benchmarks (CUDA events on the caller's stream around select, exchange and
+ * finalize of every call between begin and end); end synchronises the stream and returns microseconds per call. */
+int fns_b200_mg_profile_begin(fns_b200_mg * m, int max_calls);
+int fns_b200_mg_profile_end(fns_b200_mg * m, void * stream, double * select_us, double * exchange_us,
+                            double * finalize_us, int * calls);
 
 #ifdef __cplusplus
 }
