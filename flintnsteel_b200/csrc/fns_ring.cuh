@@ -18,8 +18,8 @@
 //            thread's own maximum in a register.  No flags, no running bound, no block barrier inside the loop:
 //            taking candidates on the spot under a running bound was measured and is slower (the insertions
 //            diverge inside the loop that feeds the ring).
-//   bound    k <= 512: (nearly) the k-th largest thread maximum, found by counting; larger k: the k-th largest
-//            cell maximum, by a two-round radix count over the 16-bit values
+//   bound    k <= 512: (nearly) the k-th largest thread maximum, found by counting; larger k: the k-th largest of
+//            the threads' three best cell maxima, found the same way
 //   pass 2   the cells that reach the bound (about k of them) are read again from L2 / HBM, element by element,
 //            and the keys that reach the bound go to the candidate buffer together with the penalised history ids;
 //            if equal values overflow the list or the buffer, every cell is offered again with votes and
@@ -75,67 +75,131 @@ __device__ __forceinline__ void bulk_load(void * dst_shared, const void * src_gl
                  : "memory");
 }
 
-// The k-th largest, repeats counted, of the 16-bit values v[0 .. n); 0 when n < k.  Two rounds of a 256-bin count;
-// equal bins of a warp are added up before they reach shared memory (the values crowd into few bins).  All NT
-// threads, uniform arguments; ends with the block synchronised.
+// A bound for k beyond the thread count, from more witnesses per thread: every thread takes the three largest of
+// its own cell maxima (cells are disjoint, so 3 * NT >= k different elements stand behind them), and the block finds
+// the k-th largest of these 3 * NT values bit by bit from the top: one count per bit (three compares, a warp sum,
+// one shared-memory add per warp, one barrier; three counters take turns so that none is cleared while it is read).
+// At least k cells reach the result; a thread with more than three such cells adds a few more.  0 when there are
+// fewer than k witnesses.  Cell of thread t in stage s at v[s * NT + t].
 template <int NT>
-__device__ uint32_t block_kth_u16(const uint16_t * v, int n, int k, SelectScratch & sc) {
+__device__ uint32_t block_kth_witness(const uint16_t * v, int n_stages, int k, SelectScratch & sc) {
     const int tid = threadIdx.x, lane = tid & 31;
-    if (n < k) return 0u;
+    uint32_t t0 = 0u, t1 = 0u, t2 = 0u;  // this thread's three largest cell maxima, t0 >= t1 >= t2
+#pragma unroll 4
+    for (int s = 0; s < n_stages; ++s) {
+        const uint32_t x = v[s * NT + tid];
+        const uint32_t a = max(t0, x), b = min(t0, x);
+        const uint32_t c = max(t1, b), d = min(t1, b);
+        t0 = a;
+        t1 = c;
+        t2 = max(t2, d);
+    }
+    if (tid < 3) sc.hist[tid] = 0u;
+    __syncthreads();
     uint32_t prefix = 0u;
-    int need = k;
-    for (int round = 0; round < 2; ++round) {
-        const int shift = round == 0 ? 8 : 0;
-        for (int i = tid; i < 256; i += NT) sc.hist[i] = 0u;
+#pragma unroll 1
+    for (int step = 0; step < 16; ++step) {
+        const uint32_t cand = prefix | (0x8000u >> step);
+        uint32_t cnt = (t0 >= cand ? 1u : 0u) + (t1 >= cand ? 1u : 0u) + (t2 >= cand ? 1u : 0u);
+        cnt = __reduce_add_sync(kFull, cnt);
+        uint32_t * slot = &sc.hist[step % 3];
+        if (lane == 0 && cnt) atomicAdd(slot, cnt);
         __syncthreads();
-        for (int i0 = 0; i0 < n; i0 += NT) {
-            const int i = i0 + tid;
-            const uint32_t x = i < n ? v[i] : 0u;
-            const bool in = i < n && (round == 0 || (x >> 8) == prefix);
-            const uint32_t act = __ballot_sync(kFull, in);
-            if (in) {
-                const uint32_t bin = (x >> shift) & 255u;
-                const uint32_t peers = __match_any_sync(act, bin);
-                if (lane == __ffs(peers) - 1) atomicAdd(&sc.hist[bin], (uint32_t) __popc(peers));
+        if (*(volatile uint32_t *) slot >= (uint32_t) k) prefix = cand;
+        if (tid == 0) sc.hist[(step + 2) % 3] = 0u;  // the counter of step + 2: its readers of step - 1 are past this barrier
+    }
+    __syncthreads();
+    return prefix;
+}
+
+// Merges sorted runs pairwise until one is left: `runs` runs of L keys each at a[r * L] (each descending, empty
+// slots = 0 last), every key finding its place in the merged pair by a binary search in the sibling run (keys are
+// distinct).  A merged run keeps its best `keep` keys only.  a and b alternate as source and destination; returns
+// the buffer that holds the result and sets *len to its length.  All NT threads; block synchronised on entry and exit.
+template <int NT>
+__device__ uint64_t * merge_runs(uint64_t * a, uint64_t * b, int runs, int L, int keep, int * len) {
+    while (runs > 1) {
+        const int Lout = 2 * L < keep ? 2 * L : keep;
+        const int out_runs = (runs + 1) >> 1;
+        for (int i = threadIdx.x; i < out_runs * Lout; i += NT) b[i] = 0ull;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < runs * L; idx += NT) {
+            const int r = idx / L, i = idx - r * L;
+            const uint64_t key = a[idx];
+            if (key == 0ull) continue;
+            int pos = i;
+            if ((r ^ 1) < runs) {  // (the last of an odd number of runs moves on as it is)
+                const uint64_t * sib = a + (size_t) (r ^ 1) * L;
+                int lo = 0, hi = L;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (sib[mid] > key) lo = mid + 1;
+                    else hi = mid;
+                }
+                pos += lo;
             }
+            if (pos < Lout) b[(size_t) (r >> 1) * Lout + pos] = key;
         }
         __syncthreads();
-        if (tid < 32) {
-            uint32_t c[8], s = 0;
+        uint64_t * t = a;
+        a = b;
+        b = t;
+        runs = out_runs;
+        L = Lout;
+    }
+    *len = L;
+    return a;
+}
+
+// The same when the number of runs and their length L = 1 << lg are powers of two (no division, and the four keys a
+// thread takes per round search side by side).
+template <int NT>
+__device__ uint64_t * merge_runs_pow2(uint64_t * a, uint64_t * b, int runs, int lg, int keep) {
+    while (runs > 1) {
+        const int L = 1 << lg;
+        const bool cut = 2 * L > keep;  // the merged run keeps `keep` keys (a power of two as well, or everything)
+        const int lg_out = cut ? lg : lg + 1;
+        const int Lout = 1 << lg_out;
+        const int total = runs << lg;
+        for (int i = threadIdx.x; i < (runs >> 1) * Lout; i += NT) b[i] = 0ull;
+        __syncthreads();
+        for (int base = threadIdx.x; base < total; base += 4 * NT) {
+            uint64_t key[4];
+            int lo[4], hi[4];
+            const uint64_t * sib[4];
 #pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                c[b] = sc.hist[lane * 8 + b];
-                s += c[b];
+            for (int q = 0; q < 4; ++q) {
+                const int idx = base + q * NT;
+                key[q] = idx < total ? a[idx] : 0ull;
+                sib[q] = a + ((size_t) ((idx >> lg) ^ 1) << lg);
+                lo[q] = 0;
+                hi[q] = key[q] != 0ull ? L : 0;
             }
-            uint32_t incl = s;  // values in the bins of lanes >= this one
+            for (int step = 0; step <= lg; ++step) {  // (at most lg + 1 halvings of [0, L])
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_down_sync(kFull, incl, o);
-                if (lane + o < 32) incl += t;
-            }
-            uint32_t above = incl - s;
-            if (above < (uint32_t) need && (uint32_t) need <= incl) {
-                bool found = false;
-#pragma unroll
-                for (int b = 7; b >= 0; --b) {
-                    if (!found) {
-                        if (above + c[b] >= (uint32_t) need) {
-                            sc.bucket = (uint32_t) (lane * 8 + b);
-                            sc.need = (uint32_t) need - above;
-                            found = true;
-                        } else {
-                            above += c[b];
-                        }
+                for (int q = 0; q < 4; ++q) {
+                    if (lo[q] < hi[q]) {
+                        const int mid = (lo[q] + hi[q]) >> 1;
+                        if (sib[q][mid] > key[q]) lo[q] = mid + 1;
+                        else hi[q] = mid;
                     }
                 }
             }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int idx = base + q * NT;
+                const int pos = (idx & (L - 1)) + lo[q];
+                if (key[q] != 0ull && pos < Lout) b[((size_t) (idx >> (lg + 1)) << lg_out) + pos] = key[q];
+            }
         }
         __syncthreads();
-        prefix = (prefix << 8) | sc.bucket;
-        need = (int) sc.need;
-        __syncthreads();
+        uint64_t * t = a;
+        a = b;
+        b = t;
+        runs >>= 1;
+        lg = lg_out;
     }
-    return prefix;
+    return a;
 }
 
 // Sorts a[0 .. m) (m a power of two, in shared memory) into descending order: a bitonic network, one barrier per
@@ -159,6 +223,15 @@ __device__ void block_sort_desc(uint64_t * a, int m) {
     }
 }
 
+
+#ifdef FNS_RING_TIMING
+__device__ unsigned g_ring_t[1024][16];
+#define RT(i) if (threadIdx.x == 0 && blockIdx.x < 1024) g_ring_t[blockIdx.x][i] = (unsigned) (clock64() - rt0);
+#define RT0 const long long rt0 = clock64();
+#else
+#define RT(i)
+#define RT0
+#endif
 
 constexpr int kRegOwn = 4;  // owned history ids that a thread keeps in registers (4 * 512 per row)
 
@@ -239,6 +312,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     // too).  Nothing is read from global memory before the previous kernel has finished.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    RT0
     // without a mask every chunk is wanted: the first stages start now
     if (tid == 0 && !mrow)
         for (int u = 0; u < depth && u < n_stages; ++u) issue_stage(u, u, 0xffffu);
@@ -395,6 +469,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         my_val[r] = 0u;
     }
 
+    RT(0)
     // 3. The streaming pass.
     float tmax = -INFINITY;     // this thread's maximum so far
     uint64_t best = 0ull;       // k == 1: this thread's best key
@@ -453,9 +528,14 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                         xv[j][2 * q + 1] = __uint_as_float(w4[q] & 0xffff0000u);
                     }
                 }
-                const uint32_t vb = bits >> (v * VEC);
+                if (bits == 0xffffu) {  // the whole cell is allowed: nothing but maxima (the same in all 16 elements' bits)
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) m = fmaxf(m, ((vb >> e) & 1u) ? xv[j][e] : -INFINITY);
+                    for (int e = 0; e < VEC; ++e) m = fmaxf(m, xv[j][e]);
+                } else {
+                    const uint32_t vb = bits >> (v * VEC);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) m = fmaxf(m, ((vb >> e) & 1u) ? xv[j][e] : -INFINITY);
+                }
             }
             if (__builtin_expect(!(m <= FLT_MAX), 0)) {  // +inf among the allowed: never a candidate (src/kernels.cu:629-639)
                 m = -INFINITY;
@@ -514,6 +594,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     if (gave_up && a.err) atomicExch(a.err, 3);  // a copy never arrived: the result of this row is not valid
     __syncthreads();  // the ring is free: what follows lives there
+    RT(1)
 
     uint64_t * buf = reinterpret_cast<uint64_t *>(ring);
     uint64_t * sel = buf + a.cap;
@@ -541,11 +622,13 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     if (k <= NT) {
         thr_v = bound_from_maxima(-FLT_MAX);
     } else {
-        const uint32_t b = block_kth_u16<NT>(cmax, n_stages * NT, k, sh.sc);
+        static_assert(FNS_B200_MAX_K <= 3 * NT, "three witnesses per thread cover the largest k");
+        const uint32_t b = block_kth_witness<NT>(cmax, n_stages, k, sh.sc);
         if (b >= 0x0080u) thr_v = word_value(b << 16);
         thr_v += 0.0f;
     }
     uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
+    RT(2)
 
     // 5. The candidates.
     auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add
@@ -580,6 +663,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     copy_word_wait();
     __syncthreads();
+    RT(3)
     for (int attempt = 0; attempt < 2; ++attempt) {
         const bool careful = attempt == 1;
         // (a) the ragged end
@@ -698,6 +782,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                 }
             }
         }
+        RT(4)
         // (c) the listed cells, one vector per thread and round, read again.  The careful way walks every cell
         // instead, a round of NT cells at a time, with a vote after each round.
         bool listed = true;
@@ -705,21 +790,59 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
             {
                 const int n_work = (int) sh.n_vl;
                 listed = n_work <= a.list_cap;  // uniform
+                const int total = listed ? n_work * NVEC : 0;
+                constexpr int PB = 2;  // items per thread whose loads are in flight together
 #pragma unroll 1
-                for (int i = tid; i < n_work * NVEC && listed; i += NT) {
-                    const uint32_t cell = vlist[i / NVEC];
-                    const int v = i % NVEC;
-                    const uint32_t bits = ((uint32_t) eff16[cell] >> (v * VEC)) & kVecBits;
-                    if (!bits) continue;
-                    const uint32_t e = cell * kCell + (uint32_t) (v * VEC);
-                    float xv[VEC];
-                    load_vec<T, VEC>(x + e, xv);
+                for (int i0 = warp * 32; i0 < total; i0 += PB * NT) {  // (the same rounds for every lane of a warp)
+                    float xv[PB][VEC];
+                    uint32_t bits[PB], e0[PB];
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        if (!(((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX)) continue;
-                        const uint64_t key = make_key(xv[j], id0 + e + (uint32_t) j);
-                        if (k == 1) best = key > best ? key : best;
-                        else if (key >= thr_key) push(key, buf, sh, a.cap);
+                    for (int q = 0; q < PB; ++q) {
+                        const int i = i0 + q * NT + lane;
+                        bits[q] = 0u;
+                        e0[q] = 0u;
+                        if (i < total) {
+                            const uint32_t cell = vlist[i / NVEC];
+                            const int v = i % NVEC;
+                            bits[q] = ((uint32_t) eff16[cell] >> (v * VEC)) & kVecBits;
+                            e0[q] = cell * kCell + (uint32_t) (v * VEC);
+                            if (bits[q]) load_vec<T, VEC>(x + e0[q], xv[q]);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < PB; ++q) {
+                        uint32_t hit = 0u;  // the elements of this vector that reach the bound
+                        if (bits[q]) {
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j)
+                                hit |= (((bits[q] >> j) & 1u) && xv[q][j] >= thr_v && xv[q][j] <= FLT_MAX) ? 1u << j : 0u;
+                        }
+                        if (k == 1) {
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) {
+                                if (!((hit >> j) & 1u)) continue;
+                                const uint64_t key = make_key(xv[q][j], id0 + e0[q] + (uint32_t) j);
+                                best = key > best ? key : best;
+                            }
+                            continue;
+                        }
+                        if (!__ballot_sync(kFull, hit != 0u)) continue;
+                        const uint32_t mine_n = (uint32_t) __popc(hit);  // one reservation per warp
+                        uint32_t upto = mine_n;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t t = __shfl_up_sync(kFull, upto, o);
+                            if (lane >= o) upto += t;
+                        }
+                        uint32_t at = 0u;
+                        if (lane == 31) at = atomicAdd(&sh.n_cand, upto);
+                        at = __shfl_sync(kFull, at, 31) + upto - mine_n;
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) {
+                            if (!((hit >> j) & 1u)) continue;
+                            if (at < (uint32_t) a.cap) buf[at] = make_key(xv[q][j], id0 + e0[q] + (uint32_t) j);
+                            ++at;
+                        }
                     }
                 }
             }
@@ -776,6 +899,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         __syncthreads();
     }
 
+    RT(5)
     // 6. The best k in the total order, and the draw.
     p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
     int32_t * tok = a.out_tokens ? a.out_tokens + row : nullptr;
@@ -800,14 +924,49 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     const int n = (int) min(sh.n_cand, (uint32_t) a.cap);
     int got;
+    int pow2_runs = 1;  // runs of four keys that cover the buffer's contents, a power of two of them
+    while (4 * pow2_runs < n) pow2_runs <<= 1;
     if (n <= kRankSelectMax) {
         got = block_rank_select<NT>(buf, n, k, sorted);
+    } else if (8 * pow2_runs <= a.cap) {
+        // a long list (k beyond 384): sorted as it is, by merging.  Every thread orders four keys in registers, the
+        // runs of four (a power of two of them: empty runs fill up) are merged pairwise in the two halves of the
+        // buffer, and the best k of the result are the answer.
+        const int half = a.cap / 2;
+        const int runs = pow2_runs;
+        for (int r = tid; r < runs; r += NT) {
+            uint64_t q[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) q[e] = 4 * r + e < n ? buf[4 * r + e] : 0ull;
+            auto order = [&](int i, int j) {
+                if (q[i] < q[j]) {
+                    const uint64_t t = q[i];
+                    q[i] = q[j];
+                    q[j] = t;
+                }
+            };
+            order(0, 1);
+            order(2, 3);
+            order(0, 2);
+            order(1, 3);
+            order(1, 2);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) buf[4 * r + e] = q[e];
+        }
+        __syncthreads();
+        RT(6)
+        int keep = 4;  // a merged run keeps the best `keep` keys: the power of two that holds k
+        while (keep < k) keep <<= 1;
+        const uint64_t * res = merge_runs_pow2<NT>(buf, buf + half, runs, 2, keep);
+        RT(7)
+        got = n < k ? n : k;
+        for (int i = tid; i < got; i += NT) sorted[i] = res[i];
     } else {
         const uint64_t tau = block_kth_key<NT>(buf, n, k, sh.sc);
         got = block_take<NT>(buf, n, k, tau, sel, sh.sc);
         if (got <= kRankSelectMax) {
             block_rank_sort<NT>(sel, got, sorted);
-        } else {  // a long list: a sorting network beats counting
+        } else {  // (buffer nearly full of keys that all matter: a sorting network over the selected ones)
             int m = 1;
             while (m < got) m <<= 1;
             for (int i = tid; i < m; i += NT) buf[i] = i < got ? sel[i] : 0ull;  // (m <= 2 * k_cap <= cap)
@@ -818,7 +977,12 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     for (int j = got + tid; j < a.k_cap; j += NT) sorted[j] = 0ull;
     __syncthreads();
+    RT(8)
+#ifdef FNS_RING_TIMING
+    if (tid == 0 && blockIdx.x < 1024) g_ring_t[blockIdx.x][15] = (unsigned) n;
+#endif
     draw_tail<NT>(sorted, got, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
+    RT(9)
 }
 
 }  // namespace fnsb

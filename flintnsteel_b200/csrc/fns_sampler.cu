@@ -236,6 +236,79 @@ __device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, u
     return nk;
 }
 
+// The same merge for long lists (vocabulary shards: a few lists of up to 1,024 keys): every key finds its place in
+// the merged order directly.  Its rank is its position in its own list plus, for every other list, the number of
+// keys there that are larger - a binary search, since the lists are sorted; keys are distinct, so ranks are too,
+// and a key of rank < k goes straight to sorted[rank].  A thread takes up to MAXC consecutive keys of one list:
+// their positions in another list only move forward, so after the first search the rest gallop from where the
+// previous one ended.  Only the first min(len, k) keys of a list can be among the best k.  No scratch, two barriers.
+// Returns the number of candidates; sorted[nk .. k_cap) = 0.  All NT threads; block synchronised on entry and exit.
+template <int NT, int MAXC>
+__device__ int merge_ranked(const uint64_t * buf, int lists, int len, uint64_t * sorted, SelectScratch & sc, int k, int k_cap) {
+    const int tid = threadIdx.x;
+    const int m = len < k ? len : k;
+    for (int j = tid; j < k_cap; j += NT) sorted[j] = 0ull;
+    if (tid == 0) sc.count = 0u;
+    __syncthreads();
+    for (int l = tid; l < lists; l += NT) {  // how many candidates there are at all (empty slots sit at the end)
+        const uint64_t * a = buf + (size_t) l * len;
+        int lo = 0, hi = m;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (a[mid] != 0ull) lo = mid + 1;
+            else hi = mid;
+        }
+        if (lo) atomicAdd(&sc.count, (uint32_t) lo);
+    }
+    int chunk = (lists * m + NT - 1) / NT;
+    chunk = chunk < 1 ? 1 : (chunk > MAXC ? MAXC : chunk);
+    const int per_list = (m + chunk - 1) / chunk;
+    for (int c = tid; c < lists * per_list; c += NT) {
+        const int l = c / per_list, j0 = (c - l * per_list) * chunk;
+        const uint64_t * mine = buf + (size_t) l * len;
+        const int n_e = chunk < m - j0 ? chunk : m - j0;
+        uint64_t x[MAXC];
+        int rank[MAXC];
+#pragma unroll
+        for (int e = 0; e < MAXC; ++e) {
+            x[e] = e < n_e ? mine[j0 + e] : 0ull;
+            rank[e] = j0 + e;
+        }
+        if (x[0] == 0ull) continue;  // sorted, empty slots last: the whole chunk is empty
+        for (int l2 = 0; l2 < lists; ++l2) {
+            if (l2 == l) continue;
+            const uint64_t * other = buf + (size_t) l2 * len;
+            int pos = 0;  // keys of `other` larger than the key at hand
+#pragma unroll
+            for (int e = 0; e < MAXC; ++e) {
+                if (x[e] == 0ull) continue;
+                int lo = pos, hi = m;
+                if (e > 0) {  // gallop: the answer is seldom far from the previous one
+                    int step = 1;
+                    while (lo + step <= m && other[lo + step - 1] > x[e]) {
+                        lo += step;
+                        step <<= 1;
+                    }
+                    hi = lo + step - 1 < m ? lo + step - 1 : m;
+                }
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (other[mid] > x[e]) lo = mid + 1;
+                    else hi = mid;
+                }
+                pos = lo;
+                rank[e] += pos;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < MAXC; ++e)
+            if (x[e] != 0ull && rank[e] < k) sorted[rank[e]] = x[e];
+    }
+    __syncthreads();
+    const int total = (int) sc.count;
+    return total < k ? total : k;
+}
+
 // The tail of k_sample (src/kernels.cu:698-720) over the nk sorted candidates: candidate softmax, top-p / min-p
 // cut, temperature weights, Philox draw.  exp and the quotients are per-element and run in parallel; the three
 // running sums keep the reference's left-to-right order: `sum` then `cum` on thread 0, the weight prefix (which
@@ -340,7 +413,10 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         if (lane == 0) *out_token = key_id(sorted[pick]);
         return;
     }
-    // More candidates: the two exponentials of a candidate go to different halves of the block.
+    // More candidates (only with k_cap > 64, which the reference does not have: there the summation order is ours to
+    // choose).  The two exponentials of a candidate go to different halves of the block; the two running sums - the
+    // candidate probabilities and the temperature weights - are made together by a blocked scan: every thread adds
+    // up its own few consecutive entries, a warp scan joins the threads, the warps' totals join the warps.
     {
         const bool second = tid >= NT / 2;
         for (int j = second ? tid - NT / 2 : tid; j < nk; j += NT / 2) {
@@ -349,44 +425,49 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
             else pj[j] = exp(d);
         }
     }
-    __syncthreads();
-    volatile double * sum_slot = reinterpret_cast<volatile double *>(&sc.hist[0]);
-    if (tid == 0) {  // left to right, as the reference adds; eight loads ahead of the additions
-        double sum = 0.0;
-        int j = 0;
-        for (; j + 8 <= nk; j += 8) {
-            double t[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) t[u] = pj[j + u];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) sum += t[u];
-        }
-        for (; j < nk; ++j) sum += pj[j];
-        *sum_slot = sum;
-    } else if (tid == 32) {
-        double run = 0.0;
-        int j = 0;
-        for (; j + 8 <= nk; j += 8) {
-            double t[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) t[u] = acc[j + u];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                run += t[u];
-                acc[j + u] = run;
-            }
-        }
-        for (; j < nk; ++j) {
-            run += acc[j];
-            acc[j] = run;
-        }
-    } else if (tid == 64) {  // the uniform does not depend on the sums
-        reinterpret_cast<volatile double *>(&sc.hist[0])[1] = philox_uniform(p.seed, p.counter);
-    }
+    if (tid == 0) reinterpret_cast<volatile double *>(&sc.hist[0])[1] = philox_uniform(p.seed, p.counter);
     __syncthreads();
     {
-        const double sum = *sum_slot;
-        for (int j = tid; j < nk; j += NT) qj[j] = pj[j] / sum;
+        constexpr int kWarpsT = NT / 32;
+        double * warp_p = reinterpret_cast<double *>(&sc.hist[16]);   // [kWarpsT] totals of the warps' probabilities
+        double * warp_w = warp_p + kWarpsT;                            // [kWarpsT] ... of their weights
+        static_assert(16 + 4 * kWarpsT <= 256, "the warps' totals fit the scratch histogram");
+        const int per = (nk + NT - 1) / NT;  // consecutive entries per thread
+        const int j0 = tid * per;
+        double sp = 0.0, sw = 0.0;
+        for (int j = j0; j < j0 + per && j < nk; ++j) {
+            sp += pj[j];
+            sw += acc[j];
+            qj[j] = sp;   // running sums inside the thread's stretch; the offsets follow
+            acc[j] = sw;
+        }
+        double ip = sp, iw = sw;  // inclusive over the lanes of the warp
+        const int lane_t = tid & 31, warp_t = tid >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double tp = __shfl_up_sync(kFull, ip, o), tw = __shfl_up_sync(kFull, iw, o);
+            if (lane_t >= o) {
+                ip += tp;
+                iw += tw;
+            }
+        }
+        if (lane_t == 31) {
+            warp_p[warp_t] = ip;
+            warp_w[warp_t] = iw;
+        }
+        __syncthreads();
+        double op = ip - sp, ow = iw - sw;  // what precedes this thread's stretch
+        for (int w = 0; w < warp_t; ++w) {
+            op += warp_p[w];
+            ow += warp_w[w];
+        }
+        for (int j = j0; j < j0 + per && j < nk; ++j) {
+            qj[j] += op;
+            acc[j] += ow;
+        }
+        __syncthreads();
+        const double sum = qj[nk - 1];
+        for (int j = tid; j < nk; j += NT) qj[j] = qj[j] / sum;  // the running probability
     }
     volatile uint32_t * first_cut = &sc.hist[8];   // first j + 1 whose running probability reaches top_p
     volatile uint32_t * first_low = &sc.hist[9];   // first j >= 1 whose probability is below min_p
@@ -395,25 +476,6 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         *first_cut = (uint32_t) nk;
         *first_low = (uint32_t) nk;
         *first_hit = 0xffffffffu;
-    }
-    __syncthreads();
-    if (tid == 0) {  // the running probability, left to right; the decisions on it are taken by everybody afterwards
-        double run = 0.0;
-        int j = 0;
-        for (; j + 8 <= nk; j += 8) {
-            double t[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) t[u] = qj[j + u];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                run += t[u];
-                qj[j + u] = run;
-            }
-        }
-        for (; j < nk; ++j) {
-            run += qj[j];
-            qj[j] = run;
-        }
     }
     __syncthreads();
     // `cum >= top_p` first holds at the smallest such j (the sums never decrease); min_p keeps the longest prefix of
@@ -1293,7 +1355,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
 namespace fnsb {
 
 // ---- finalize as a kernel of its own -------------------------------------------------------------------------
-constexpr int kFinalThreads = 256;
+constexpr int kFinalThreads = 512;
 
 struct FinalArgs {
     const fns_b200_cand * cands;  // entry j of list l of row r at r * row_stride + l * list_stride + j
@@ -1333,8 +1395,27 @@ __global__ void __launch_bounds__(kFinalThreads) k_finalize(const FinalArgs a) {
         buf[i] = cand_to_key(a.cands[row_base + (size_t) l * a.list_stride + j]);
     }
     __syncthreads();
-    const int nk = merge_lists<kFinalThreads>(buf, a.lists, a.list_len, sel, sorted, reinterpret_cast<uint64_t *>(pj),
-                                              2 * a.k_cap, sh.sc, k, a.k_cap);
+    // many short lists: witnesses and counting; a few long ones (vocabulary shards): merged pairwise, every key
+    // finding its place in the sibling list by a binary search, a merged list keeping its best k
+    int nk;
+    if (a.list_len > 64 && k <= a.list_len) {  // (then a merged list is never longer than list_len: the halves fit)
+        uint64_t * spare = reinterpret_cast<uint64_t *>(&sh + 1);  // [lists * list_len / 2 + k]
+        int len = 0;
+        const uint64_t * res = merge_runs<kFinalThreads>(buf, spare, a.lists, a.list_len, k, &len);
+        if (tid == 0) sh.sc.count = 0u;
+        __syncthreads();
+        const int take = len < k ? len : k;
+        for (int j = tid; j < a.k_cap; j += kFinalThreads) {
+            const uint64_t key = j < take ? res[j] : 0ull;
+            sorted[j] = key;
+            if (key != 0ull && (j + 1 == take || res[j + 1] == 0ull)) sh.sc.count = (uint32_t) j + 1u;  // the last candidate
+        }
+        __syncthreads();
+        nk = (int) sh.sc.count;
+    } else {
+        nk = merge_lists<kFinalThreads>(buf, a.lists, a.list_len, sel, sorted, reinterpret_cast<uint64_t *>(pj), 2 * a.k_cap,
+                                        sh.sc, k, a.k_cap);
+    }
     draw_tail<kFinalThreads>(sorted, nk, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap,
                              a.out_tokens ? a.out_tokens + row : nullptr,
                              a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr);
@@ -1520,7 +1601,9 @@ bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int h
 }
 
 size_t final_smem(int lists, int list_len, int k_cap) {
-    return (size_t) lists * list_len * 8 + (size_t) k_cap * 8 * 4 + sizeof(FinalShared) + 16;
+    // all keys | staging, sorted, p, acc | scratch | (long lists) the other half of the pairwise merge
+    const size_t spare = list_len > 64 ? ((size_t) (lists + 1) / 2 * list_len + k_cap) * 8 : 0;
+    return (size_t) lists * list_len * 8 + (size_t) k_cap * 8 * 4 + sizeof(FinalShared) + 16 + spare;
 }
 
 // Every kernel that a sampling call can launch opts in to large dynamic shared memory, once per device, before the
@@ -1833,6 +1916,14 @@ int fns_b200_device_status(fns_b200_sampler * s, void * stream) {
     }
     return FNS_B200_OK;
 }
+
+#ifdef FNS_RING_TIMING
+int fns_b200_debug_ring_times(unsigned * out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, fnsb::g_ring_t, sizeof(unsigned) * 1024 * 16);
+    return 0;
+}
+#endif
 
 int fns_b200_hint_host_logits(fns_b200_sampler * s, int on) {
     if (!s) return FNS_B200_ERR_ARG;
