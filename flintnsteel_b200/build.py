@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfns_b200.so")
-SOURCES = ["fns_sampler.cu", "fns_compat.cu", "fns_engine.cu", "fns_mg.cu"]
+SOURCES = ["fns_sampler.cu", "fns_compat.cu", "fns_engine.cu", "fns_mg.cu", "fns_driver.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17",
@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "-shared",
     "-cudart", "static",
-    "--threads", "4",
+    "--threads", "5",
 ]
 
 

@@ -15,6 +15,8 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <unordered_map>
+#include <vector>
 
 #include "fns_internal.h"
 
@@ -44,6 +46,7 @@ struct Slot {
     int32_t * tokens_h;
     int32_t * draft_h;
     int32_t * accept_h;
+    int32_t * mask_rows_h;
     // device copies
     uint32_t * masks_d;
     int32_t * history_d;
@@ -52,6 +55,7 @@ struct Slot {
     int32_t * tokens_d;
     int32_t * draft_d;
     int32_t * accept_d;
+    int32_t * mask_rows_d;
     cudaEvent_t done;
     int rows;
     bool busy;
@@ -71,6 +75,15 @@ struct fns_b200_engine {
     int32_t * counts_d;
     int32_t * counts_h;
     const int32_t * last_tokens;
+    // masks kept on the device by grammar state: slot 0 allows everything, slots 1 .. cache_slots hold states
+    uint32_t * cache_d;               // [cache_slots + 1][words]
+    int cache_slots;
+    uint64_t tick;
+    std::vector<uint64_t> slot_state; // [cache_slots + 1] the state a slot holds
+    std::vector<uint64_t> slot_used;  // ... and when it was last asked for
+    std::vector<uint8_t> slot_filled;
+    std::unordered_map<uint64_t, int> * by_state;
+    int64_t mask_bytes_uploaded, mask_hits, mask_misses;
     char msg[256];
 };
 
@@ -97,9 +110,9 @@ bool alloc_pair(T ** host, T ** dev, size_t count) {
 
 void free_slot(Slot & s) {
     cudaFreeHost(s.masks_h); cudaFreeHost(s.history_h); cudaFreeHost(s.history_len_h); cudaFreeHost(s.params_h);
-    cudaFreeHost(s.tokens_h); cudaFreeHost(s.draft_h); cudaFreeHost(s.accept_h);
+    cudaFreeHost(s.tokens_h); cudaFreeHost(s.draft_h); cudaFreeHost(s.accept_h); cudaFreeHost(s.mask_rows_h);
     cudaFree(s.masks_d); cudaFree(s.history_d); cudaFree(s.history_len_d); cudaFree(s.params_d);
-    cudaFree(s.tokens_d); cudaFree(s.draft_d); cudaFree(s.accept_d);
+    cudaFree(s.tokens_d); cudaFree(s.draft_d); cudaFree(s.accept_d); cudaFree(s.mask_rows_d);
     if (s.done) cudaEventDestroy(s.done);
 }
 
@@ -169,6 +182,7 @@ int fns_b200_engine_create(int device, int max_rows, int vocab, int k_cap, int m
              alloc_pair(&s.history_h, &s.history_d, hist) && alloc_pair(&s.history_len_h, &s.history_len_d, max_rows) &&
              alloc_pair(&s.params_h, &s.params_d, max_rows) && alloc_pair(&s.tokens_h, &s.tokens_d, max_rows) &&
              alloc_pair(&s.draft_h, &s.draft_d, max_rows) && alloc_pair(&s.accept_h, &s.accept_d, max_rows) &&
+             alloc_pair(&s.mask_rows_h, &s.mask_rows_d, max_rows) &&
              cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming) == cudaSuccess;
     }
     ok = ok && cudaMalloc(&e->sess_history, hist * sizeof(int32_t)) == cudaSuccess &&
@@ -194,12 +208,15 @@ int fns_b200_engine_destroy(fns_b200_engine * e) {
     cudaFree(e->sess_history_len);
     cudaFree(e->counts_d);
     cudaFreeHost(e->counts_h);
+    cudaFree(e->cache_d);
+    delete e->by_state;
     fns_b200_destroy(e->sampler);
     delete e;
     return FNS_B200_OK;
 }
 
 const char * fns_b200_engine_last_error(const fns_b200_engine * e) { return e ? e->msg : "null engine"; }
+int fns_b200_engine_words(const fns_b200_engine * e) { return e ? e->words : 0; }
 fns_b200_sampler * fns_b200_engine_sampler(fns_b200_engine * e) { return e ? e->sampler : nullptr; }
 const int32_t * fns_b200_engine_device_tokens(const fns_b200_engine * e) { return e ? e->last_tokens : nullptr; }
 
@@ -262,6 +279,150 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
     if (rc != FNS_B200_OK) return esampler(e, rc);
     if ((err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) !=
             cudaSuccess ||
+        (err = cudaEventRecord(s.done, st)) != cudaSuccess)
+        return ecuda(e, err, "token copy");
+    s.rows = rows;
+    s.busy = true;
+    e->last_tokens = s.tokens_d;
+    e->head = (e->head + 1) % kSlots;
+    return FNS_B200_OK;
+}
+
+// ---- the bitmask as its producer hands it over: xgrammar's DLTensor, with a device-side cache by grammar state ------
+int fns_b200_mask_view(const fns_b200_dl_tensor * t, int vocab, int * rows, const uint32_t ** words_host, int64_t * stride_words) {
+    if (!t || !rows || !words_host || !stride_words || vocab <= 0) return FNS_B200_ERR_ARG;
+    const int words = (vocab + 31) / 32;
+    // what xgrammar fills (tools/fns_serve/fns_serve.cpp:313-321): int32, on the CPU, [words] or [rows][words]
+    if (!t->data || (t->device_type != 1 /* kDLCPU */ && t->device_type != 3 /* kDLCUDAHost */)) return FNS_B200_ERR_ARG;
+    if (t->dtype_bits != 32 || t->dtype_lanes != 1 || (t->dtype_code != 0 /* kDLInt */ && t->dtype_code != 1 /* kDLUInt */))
+        return FNS_B200_ERR_ARG;
+    if ((t->ndim != 1 && t->ndim != 2) || !t->shape || t->shape[t->ndim - 1] != words) return FNS_B200_ERR_ARG;
+    if (t->strides && t->strides[t->ndim - 1] != 1) return FNS_B200_ERR_ARG;  // words of a row side by side
+    *rows = t->ndim == 2 ? (int) t->shape[0] : 1;
+    *stride_words = t->ndim == 2 && t->strides ? t->strides[0] : words;
+    if (*rows <= 0 || *stride_words < words) return FNS_B200_ERR_ARG;
+    *words_host = reinterpret_cast<const uint32_t *>(static_cast<const char *>(t->data) + t->byte_offset);
+    return FNS_B200_OK;
+}
+
+int fns_b200_engine_mask_cache(fns_b200_engine * e, int slots) {
+    if (!e || slots < 0 || slots > 65535) return FNS_B200_ERR_ARG;
+    Dev g(e->device);
+    if (e->slot[0].busy || e->slot[1].busy) return efail(e, FNS_B200_ERR_ARG, "mask_cache: picks in flight");
+    cudaFree(e->cache_d);
+    e->cache_d = nullptr;
+    e->cache_slots = 0;
+    delete e->by_state;
+    e->by_state = nullptr;
+    if (slots == 0) return FNS_B200_OK;
+    cudaError_t err = cudaMalloc(&e->cache_d, (size_t) (slots + 1) * e->words * sizeof(uint32_t));
+    if (err == cudaSuccess) err = cudaMemset(e->cache_d, 0xff, (size_t) e->words * sizeof(uint32_t));  // slot 0: every id allowed
+    if (err != cudaSuccess) return ecuda(e, err, "mask cache");
+    e->cache_slots = slots;
+    e->slot_state.assign(slots + 1, 0);
+    e->slot_used.assign(slots + 1, 0);
+    e->slot_filled.assign(slots + 1, 0);
+    e->by_state = new std::unordered_map<uint64_t, int>();
+    e->mask_bytes_uploaded = e->mask_hits = e->mask_misses = 0;
+    return FNS_B200_OK;
+}
+
+int fns_b200_engine_mask_stats(const fns_b200_engine * e, int64_t * hits, int64_t * misses, int64_t * bytes_uploaded) {
+    if (!e) return FNS_B200_ERR_ARG;
+    if (hits) *hits = e->mask_hits;
+    if (misses) *misses = e->mask_misses;
+    if (bytes_uploaded) *bytes_uploaded = e->mask_bytes_uploaded;
+    return FNS_B200_OK;
+}
+
+int fns_b200_engine_pick_async_dl(fns_b200_engine * e, const void * logits, int dtype, int64_t row_stride, int rows,
+                                  const fns_b200_dl_tensor * masks, const uint64_t * mask_states_host,
+                                  const fns_b200_params * params_host, void * stream) {
+    if (!e) return FNS_B200_ERR_ARG;
+    if (!logits || !params_host || rows <= 0) return efail(e, FNS_B200_ERR_ARG, "logits / params null or rows <= 0");
+    if (rows > e->max_rows) return efail(e, FNS_B200_ERR_CAPACITY, "rows beyond the engine's limit");
+    const uint32_t * words_host = nullptr;
+    int mask_rows = 0;
+    int64_t mstride = 0;
+    if (masks) {
+        if (fns_b200_mask_view(masks, e->vocab, &mask_rows, &words_host, &mstride) != FNS_B200_OK)
+            return efail(e, FNS_B200_ERR_ARG, "masks: not an int32 CPU tensor of [rows][ceil(vocab / 32)] (or [ceil(vocab / 32)])");
+        if (mask_rows != rows && mask_rows != 1) return efail(e, FNS_B200_ERR_ARG, "masks: one row, or one row per logit row");
+    }
+    if (!mask_states_host || !masks) {  // no cache: the plain path; rows of a strided tensor are packed on the way
+        if (!masks) return fns_b200_engine_pick_async(e, logits, 0, dtype, row_stride, rows, nullptr, nullptr, 0, nullptr, params_host, stream);
+        if (mask_rows == rows && mstride == e->words)
+            return fns_b200_engine_pick_async(e, logits, 0, dtype, row_stride, rows, words_host, nullptr, 0, nullptr, params_host, stream);
+        Slot & s = e->slot[e->head];
+        if (s.busy) return efail(e, FNS_B200_ERR_ARG, "two picks already in flight: call pick_wait first");
+        std::vector<uint32_t> packed((size_t) rows * e->words);
+        for (int r = 0; r < rows; ++r)
+            std::memcpy(packed.data() + (size_t) r * e->words, words_host + (size_t) (mask_rows == 1 ? 0 : r) * mstride, (size_t) e->words * 4);
+        return fns_b200_engine_pick_async(e, logits, 0, dtype, row_stride, rows, packed.data(), nullptr, 0, nullptr, params_host, stream);
+    }
+    if (!e->cache_d) return efail(e, FNS_B200_ERR_ARG, "mask states given but no cache: call fns_b200_engine_mask_cache first");
+    Dev g(e->device);
+    cudaStream_t st = (cudaStream_t) stream;
+    Slot & s = e->slot[e->head];
+    if (s.busy) return efail(e, FNS_B200_ERR_ARG, "two picks already in flight: call pick_wait first");
+    // a row's state either sits in a slot already (nothing moves), or takes the slot that has waited longest
+    cudaError_t err = cudaSuccess;
+    int staged = 0;
+    ++e->tick;
+    for (int r = 0; r < rows; ++r) {  // first the states that are here already: none of them may be pushed out by this call
+        auto it = e->by_state->find(mask_states_host[r]);
+        if (mask_states_host[r] != FNS_B200_NO_MASK && it != e->by_state->end()) e->slot_used[it->second] = e->tick;
+    }
+    for (int r = 0; r < rows; ++r) {
+        const uint64_t state = mask_states_host[r];
+        if (state == FNS_B200_NO_MASK) {
+            s.mask_rows_h[r] = 0;
+            continue;
+        }
+        auto it = e->by_state->find(state);
+        int slot;
+        if (it != e->by_state->end()) {
+            slot = it->second;
+            ++e->mask_hits;
+        } else {
+            slot = -1;
+            uint64_t oldest = ~0ull;
+            for (int c = 1; c <= e->cache_slots; ++c) {
+                if (!e->slot_filled[c]) {
+                    slot = c;
+                    break;
+                }
+                if (e->slot_used[c] < e->tick && e->slot_used[c] < oldest) {  // (a slot asked for in this call stays)
+                    oldest = e->slot_used[c];
+                    slot = c;
+                }
+            }
+            if (slot < 0) return efail(e, FNS_B200_ERR_CAPACITY, "more distinct grammar states in one call than cache slots");
+            if (e->slot_filled[slot]) e->by_state->erase(e->slot_state[slot]);
+            (*e->by_state)[state] = slot;
+            e->slot_state[slot] = state;
+            e->slot_filled[slot] = 1;
+            // through pinned staging (the producer's buffer is pageable and refilled for the next token)
+            uint32_t * stage_at = s.masks_h + (size_t) staged * e->words;
+            std::memcpy(stage_at, words_host + (size_t) (mask_rows == 1 ? 0 : r) * mstride, (size_t) e->words * 4);
+            err = cudaMemcpyAsync(e->cache_d + (size_t) slot * e->words, stage_at, (size_t) e->words * 4, cudaMemcpyHostToDevice, st);
+            if (err != cudaSuccess) return ecuda(e, err, "mask upload");
+            ++staged;
+            ++e->mask_misses;
+            e->mask_bytes_uploaded += (int64_t) e->words * 4;
+        }
+        e->slot_used[slot] = e->tick;
+        s.mask_rows_h[r] = slot;
+    }
+    if ((err = cudaMemcpyAsync(s.mask_rows_d, s.mask_rows_h, (size_t) rows * sizeof(int32_t), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (err = stage(s.params_h, s.params_d, params_host, (size_t) rows, st)) != cudaSuccess)
+        return ecuda(e, err, "mask rows / params copy");
+    const bool hist = e->max_history > 0;
+    const int rc = fns_b200_sample_rows_shared_masks(e->sampler, logits, dtype, row_stride, e->vocab, rows, e->cache_d, e->words,
+                                                     s.mask_rows_d, hist ? e->sess_history : nullptr, hist ? e->max_history : 0,
+                                                     hist ? e->sess_history_len : nullptr, s.params_d, s.tokens_d, st);
+    if (rc != FNS_B200_OK) return esampler(e, rc);
+    if ((err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) != cudaSuccess ||
         (err = cudaEventRecord(s.done, st)) != cudaSuccess)
         return ecuda(e, err, "token copy");
     s.rows = rows;

@@ -269,7 +269,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     unsigned char * ring = smem_raw + a.ring_off;
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride;
-    const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride : nullptr;
     const uint32_t id0 = (uint32_t) a.id_base;
 
     // What the copy of one stage moves: whole 16-byte vectors only (a ragged end is fetched with plain loads).
@@ -312,6 +311,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     // too).  Nothing is read from global memory before the previous kernel has finished.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const uint32_t * mrow = a.masks ? a.masks + (size_t) (a.mask_rows ? a.mask_rows[row] : row) * a.mask_stride : nullptr;
     RT0
     // without a mask every chunk is wanted: the first stages start now
     if (tid == 0 && !mrow)

@@ -55,6 +55,7 @@ struct SelectArgs {
     int id_base;
     const uint32_t * masks;
     int64_t mask_stride;
+    const int32_t * mask_rows;  // null, or per row: which row of `masks` holds its mask (rows may share one)
     const int32_t * history;
     int64_t history_stride;
     const int32_t * history_len;
@@ -595,13 +596,13 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
     SelectShared & sh = *reinterpret_cast<SelectShared *>(segpos + a.seg_cap);
 
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
-    const uint32_t * mrow = a.masks ? a.masks + (size_t) row * a.mask_stride + (lo >> 5) : nullptr;
     const uint32_t id0 = (uint32_t) (a.id_base + lo);
     // Launched with programmatic stream serialisation: this block may start while the previous kernel of the stream
     // still drains, and the next kernel's blocks may take the places of blocks that have exited (they wait here
     // too).  Nothing is read from global memory before the previous kernel has finished.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const uint32_t * mrow = a.masks ? a.masks + (size_t) (a.mask_rows ? a.mask_rows[row] : row) * a.mask_stride + (lo >> 5) : nullptr;
 
     // Everything whose address is known is requested before anything is waited for: the row's parameters, its
     // history length, the first history ids and the mask words.
@@ -1731,7 +1732,7 @@ struct DeviceGuard {
 
 // Shared front end of sample_rows / select_rows / verify_accept: argument checks, plan, the select launch.
 int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
-               int32_t id_base, const uint32_t * masks, int64_t mask_stride, const int32_t * history,
+               int32_t id_base, const uint32_t * masks, int64_t mask_stride, const int32_t * mask_rows, const int32_t * history,
                int64_t history_stride, const int32_t * history_len, const int32_t * draft, int n_draft,
                const fns_b200_params * params, const fns_b200_params * p0, int32_t * out_tokens,
                fns_b200_cand * out_cands, cudaStream_t st, Plan & pl) {
@@ -1760,6 +1761,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.id_base = id_base;
     a.masks = masks;
     a.mask_stride = mask_stride;
+    a.mask_rows = masks ? mask_rows : nullptr;
     a.history = history;
     a.history_stride = history_stride;
     a.history_len = history_len;
@@ -1962,9 +1964,21 @@ int fns_b200_sample_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     if (!out_tokens || !params) return fail(s, FNS_B200_ERR_ARG, "out_tokens or params null");
     DeviceGuard g(s->device);
     Plan pl;
-    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
+    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, nullptr, history, history_stride,
                         history_len, nullptr, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
     return rc;
+}
+
+int fns_b200_sample_rows_shared_masks(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab,
+                                      int rows, const uint32_t * masks, int64_t mask_stride_words, const int32_t * mask_rows,
+                                      const int32_t * history, int64_t history_stride, const int32_t * history_len,
+                                      const fns_b200_params * params, int32_t * out_tokens, void * stream) {
+    if (!s) return FNS_B200_ERR_ARG;
+    if (!out_tokens || !params || !masks || !mask_rows) return fail(s, FNS_B200_ERR_ARG, "out_tokens, params, masks or mask_rows null");
+    DeviceGuard g(s->device);
+    Plan pl;
+    return run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, mask_rows, history, history_stride,
+                      history_len, nullptr, 0, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
 }
 
 int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
@@ -1975,7 +1989,7 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
     if (history && history_len > 0) return fail(s, FNS_B200_ERR_ARG, "sample_one takes no history: use sample_rows");
     DeviceGuard g(s->device);
     Plan pl;
-    int rc = run_select(s, logits, dtype, vocab, vocab, 1, 0, mask, (vocab + 31) / 32, nullptr, 0, nullptr, nullptr, 0,
+    int rc = run_select(s, logits, dtype, vocab, vocab, 1, 0, mask, (vocab + 31) / 32, nullptr, nullptr, 0, nullptr, nullptr, 0,
                         nullptr, params_host, out_token, nullptr, (cudaStream_t) stream, pl);
     return rc;
 }
@@ -1988,7 +2002,7 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
     if (!out_cands || !params) return fail(s, FNS_B200_ERR_ARG, "out_cands or params null");
     DeviceGuard g(s->device);
     Plan pl;
-    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, id_base, masks, mask_stride_words, history,
+    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, id_base, masks, mask_stride_words, nullptr, history,
                         history_stride, history_len, nullptr, 0, params, nullptr, nullptr, out_cands,
                         (cudaStream_t) stream, pl);
     return rc;
@@ -2029,7 +2043,7 @@ int fns_b200_verify_accept(fns_b200_sampler * s, const void * logits, int dtype,
     DeviceGuard g(s->device);
     const int rows = windows * (n_draft + 1);
     Plan pl;
-    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history, history_stride,
+    int rc = run_select(s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, nullptr, history, history_stride,
                         history_len, draft, n_draft, params, nullptr, out_tokens, nullptr, (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return rc;
     k_accept<<<(unsigned) ((windows + 127) / 128), 128, 0, (cudaStream_t) stream>>>(out_tokens, draft, n_draft, windows,
@@ -2141,7 +2155,7 @@ extern "C" int fns_b200_sample_rows_noalloc(int device, const void * logits, int
     const cudaError_t e = cudaMemsetAsync(s.tickets, 0, kNoAllocRows * sizeof(unsigned) + sizeof(int), (cudaStream_t) stream);
     if (e != cudaSuccess) return fail_text(FNS_B200_ERR_CUDA, cudaGetErrorString(e));
     Plan pl;
-    const int rc = run_select(&s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, history,
+    const int rc = run_select(&s, logits, dtype, row_stride, vocab, rows, 0, masks, mask_stride_words, nullptr, history,
                               history_stride, history_len, nullptr, 0, params, nullptr, out_tokens, nullptr,
                               (cudaStream_t) stream, pl);
     if (rc != FNS_B200_OK) return fail_text(rc, s.msg);

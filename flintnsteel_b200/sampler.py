@@ -71,6 +71,21 @@ SYMBOLS = [
     "fns_b200_engine_append",
     "fns_b200_engine_verify",
     "fns_b200_lookup_draft",
+    "fns_b200_sample_rows_shared_masks",
+    "fns_b200_mask_view",
+    "fns_b200_engine_mask_cache",
+    "fns_b200_engine_mask_stats",
+    "fns_b200_engine_pick_async_dl",
+    "fns_b200_engine_words",
+    "fns_b200_lookup_draft_rows",
+    "fns_b200_spec_window_masks",
+    "fns_b200_spec_commit",
+    "fns_b200_spec_policy_init",
+    "fns_b200_spec_policy_new_request",
+    "fns_b200_spec_choose_width",
+    "fns_b200_spec_observe",
+    "fns_b200_spec_decode",
+    "fns_b200_params_from_json",
     "fns_b200_mg_unique_id",
     "fns_b200_mg_create",
     "fns_b200_mg_destroy",
@@ -154,6 +169,22 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_engine_verify.argtypes = [vp, vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp]
     lib.fns_b200_lookup_draft.argtypes = [vp, i32, i32, vp]
     lib.fns_b200_hint_host_logits.argtypes = [vp, i32]
+    i32p, i64p = ctypes.POINTER(i32), ctypes.POINTER(i64)
+    lib.fns_b200_sample_rows_shared_masks.argtypes = [vp, vp, i32, i64, i32, i32, vp, i64, vp, vp, i64, vp, vp, vp, vp]
+    lib.fns_b200_mask_view.argtypes = [vp, i32, i32p, ctypes.POINTER(vp), i64p]
+    lib.fns_b200_engine_mask_cache.argtypes = [vp, i32]
+    lib.fns_b200_engine_mask_stats.argtypes = [vp, i64p, i64p, i64p]
+    lib.fns_b200_engine_pick_async_dl.argtypes = [vp, vp, i32, i64, i32, vp, vp, vp, vp]
+    lib.fns_b200_engine_words.argtypes = [vp]
+    lib.fns_b200_lookup_draft_rows.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, vp]
+    lib.fns_b200_spec_window_masks.argtypes = [vp, vp, i32, i32, vp]
+    lib.fns_b200_spec_commit.argtypes = [vp, i32, vp, i32, vp, i32, i32, vp, vp, vp, i32p, i32p, i32p]
+    lib.fns_b200_spec_policy_init.argtypes = [vp, i32]
+    lib.fns_b200_spec_policy_new_request.argtypes = [vp]
+    lib.fns_b200_spec_choose_width.argtypes = [vp, i32]
+    lib.fns_b200_spec_observe.argtypes = [vp, i32, ctypes.c_double, i32, i32]
+    lib.fns_b200_spec_decode.argtypes = [vp, vp, vp, vp, i32, i32, vp, i32, vp, i32, i32, vp, vp, vp, vp]
+    lib.fns_b200_params_from_json.argtypes = [ctypes.c_char_p, vp]
     lib.fns_b200_mg_unique_id.argtypes = [vp]
     lib.fns_b200_mg_create.argtypes = [i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, ctypes.POINTER(vp)]
     lib.fns_b200_mg_create_with_ops.argtypes = [i32, i32, i32, i32, i32, i32, i32, vp, ctypes.POINTER(vp)]
@@ -169,6 +200,9 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_last_error.restype = ctypes.c_char_p
     lib.fns_b200_engine_last_error.restype = ctypes.c_char_p
     lib.fns_b200_mg_last_error.restype = ctypes.c_char_p
+    lib.fns_b200_spec_policy_init.restype = None
+    lib.fns_b200_spec_policy_new_request.restype = None
+    lib.fns_b200_spec_observe.restype = None
     lib.fns_b200_launch_count.restype = ctypes.c_int64
     lib.fns_b200_engine_sampler.restype = vp
     lib.fns_b200_engine_device_tokens.restype = vp
@@ -377,6 +411,27 @@ class Engine:
             logits.stride(0), rows, _host(masks_host), _host(history_host), hs, _host(history_len_host),
             _host(params_host), _stream()))
 
+    def mask_cache(self, slots: int):
+        self._check(self.lib.fns_b200_engine_mask_cache(self.handle, slots))
+
+    def mask_stats(self):
+        """(hits, misses, bytes_uploaded) of the device-side mask cache."""
+        a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        self._check(self.lib.fns_b200_engine_mask_stats(self.handle, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
+        return a.value, b.value, c.value
+
+    def words(self) -> int:
+        return int(self.lib.fns_b200_engine_words(self.handle))
+
+    def pick_async_dl(self, logits, params_host, masks=None, mask_states=None):
+        """``masks``: the producer's CPU int32 tensor ([words] or [rows][words]) or None; ``mask_states``: uint64
+        [rows] grammar-state ids for the device-side cache, or None."""
+        dl = None if masks is None else (masks if isinstance(masks, DLTensor) else DLTensor.of(masks))
+        st = None if mask_states is None else np.ascontiguousarray(mask_states, dtype=np.uint64)
+        self._check(self.lib.fns_b200_engine_pick_async_dl(
+            self.handle, ctypes.c_void_p(logits.data_ptr()), _dtype_code(logits), logits.stride(0), logits.shape[0],
+            None if dl is None else ctypes.addressof(dl), _host(st), _host(params_host), _stream()))
+
     def pick_wait(self, rows: int) -> np.ndarray:
         out = np.empty(rows, np.int32)
         self._check(self.lib.fns_b200_engine_pick_wait(self.handle, _host(out)))
@@ -405,6 +460,68 @@ class Engine:
             _host(np.ascontiguousarray(draft_host, dtype=np.int32)), _host(masks_host), _host(params_host),
             _host(tokens), _host(accept), _stream()))
         return tokens, accept
+
+
+MAX_WINDOW = 32
+
+
+class DLTensor(ctypes.Structure):
+    """``fns_b200_dl_tensor`` = the layout of DLPack's DLTensor."""
+
+    _fields_ = [("data", ctypes.c_void_p), ("device_type", ctypes.c_int32), ("device_id", ctypes.c_int32),
+                ("ndim", ctypes.c_int32), ("dtype_code", ctypes.c_uint8), ("dtype_bits", ctypes.c_uint8),
+                ("dtype_lanes", ctypes.c_uint16), ("shape", ctypes.POINTER(ctypes.c_int64)),
+                ("strides", ctypes.POINTER(ctypes.c_int64)), ("byte_offset", ctypes.c_uint64)]
+
+    @classmethod
+    def of(cls, t):
+        """View of a CPU int32 / uint32 torch tensor or numpy array (kept alive by the returned object)."""
+        import torch
+
+        if isinstance(t, np.ndarray):
+            t = torch.from_numpy(t.view(np.int32) if t.dtype == np.uint32 else t)
+        d = cls()
+        d._keep = (t, (ctypes.c_int64 * t.dim())(*t.shape), (ctypes.c_int64 * t.dim())(*t.stride()))
+        d.data, d.device_type, d.device_id, d.ndim = t.data_ptr(), 3 if t.is_pinned() else 1, 0, t.dim()
+        d.dtype_code, d.dtype_bits, d.dtype_lanes = (0 if t.dtype == torch.int32 else 2 if t.is_floating_point() else 1), \
+            t.element_size() * 8, 1
+        d.shape, d.strides, d.byte_offset = d._keep[1], d._keep[2], 0
+        return d
+
+
+class SpecCounters(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("generated", "windows", "drafted", "accepted", "emitted", "skipped", "iterations")]
+
+
+class SpecPolicy(ctypes.Structure):
+    _fields_ = [("spec", ctypes.c_int32), ("skipped_proposals", ctypes.c_int32), ("accepted", ctypes.c_uint64),
+                ("offered", ctypes.c_uint64), ("cost", ctypes.c_double * (MAX_WINDOW + 1))]
+
+
+GRAMMAR_FILL = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32))
+GRAMMAR_ACCEPT = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_int32)
+GRAMMAR_TERMINATED = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+GRAMMAR_ROLLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int)
+MODEL_FORWARD = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.c_int, ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int64))
+
+
+class Grammar(ctypes.Structure):  # fns_b200_grammar
+    _fields_ = [("user", ctypes.c_void_p), ("fill", GRAMMAR_FILL), ("accept", GRAMMAR_ACCEPT),
+                ("terminated", GRAMMAR_TERMINATED), ("rollback", GRAMMAR_ROLLBACK)]
+
+
+class Model(ctypes.Structure):  # fns_b200_model
+    _fields_ = [("user", ctypes.c_void_p), ("forward", MODEL_FORWARD)]
+
+
+def params_from_json(line: str) -> np.ndarray:
+    """The sampling fields of one request line (tools/fns_serve/fns_serve.cpp:291-303) as one ``fns_b200_params``."""
+    p = np.zeros(1, dtype=PARAMS_DTYPE)
+    rc = load_library().fns_b200_params_from_json(line.encode(), ctypes.c_void_p(p.ctypes.data))
+    if rc != OK:
+        raise SamplerError(rc, "fns_b200_params_from_json failed")
+    return p
 
 
 def lookup_draft(history, want: int) -> np.ndarray:

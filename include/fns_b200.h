@@ -101,6 +101,13 @@ int fns_b200_sample_rows(fns_b200_sampler * s, const void * logits, int dtype, i
                          int64_t history_stride, const int32_t * history_len, const fns_b200_params * params,
                          int32_t * out_tokens, void * stream);
 
+/* The same when rows share masks: row r reads the mask masks[mask_rows[r]] (device int32[rows]).  Serves a device-side
+ * cache of grammar states (fns_b200_engine_pick_async_dl): a state's mask is uploaded once and named by its slot. */
+int fns_b200_sample_rows_shared_masks(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab,
+                                      int rows, const uint32_t * masks, int64_t mask_stride_words, const int32_t * mask_rows,
+                                      const int32_t * history, int64_t history_stride, const int32_t * history_len,
+                                      const fns_b200_params * params, int32_t * out_tokens, void * stream);
+
 /* One row with parameters passed by value from the host: the shape of k::sample / k::argmax
  * (src/kernels.cuh:69,74-75).  `params_host` is read during the call. */
 int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
@@ -218,6 +225,40 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
                                int64_t row_stride, int rows, const uint32_t * masks_host,
                                const int32_t * history_host, int64_t history_stride,
                                const int32_t * history_len_host, const fns_b200_params * params_host, void * stream);
+/* The bitmask as its producer hands it over.  fns-serve gives the sampler xgrammar's own tensor: a DLTensor of int32 on
+ * the CPU with GetBitmaskSize(vocab) = ceil(vocab / 32) words, refilled per token by FillNextTokenBitmask and per
+ * window column into [W][words] (tools/fns_serve/fns_serve.cpp:306-328, 340-354; bit order tests/xgrammar_smoke.cpp:87-102).
+ * fns_b200_dl_tensor has the layout of DLTensor (dlpack.h), so a `const DLTensor *` can be passed as it is. */
+typedef struct fns_b200_dl_tensor {
+    void * data;
+    int32_t device_type; /* 1 = kDLCPU, 3 = kDLCUDAHost */
+    int32_t device_id;
+    int32_t ndim;        /* 1: [words], 2: [rows][words] */
+    uint8_t dtype_code;  /* 0 = kDLInt (what xgrammar uses), 1 = kDLUInt */
+    uint8_t dtype_bits;  /* 32 */
+    uint16_t dtype_lanes;
+    int64_t * shape;
+    int64_t * strides;   /* NULL = compact; in elements */
+    uint64_t byte_offset;
+} fns_b200_dl_tensor;
+/* Checks the tensor against the vocabulary and returns its rows, the first word and the row stride in words. */
+int fns_b200_mask_view(const fns_b200_dl_tensor * t, int vocab, int * rows, const uint32_t ** words_host, int64_t * stride_words);
+/* Keeps up to `slots` masks on the device, one per grammar state (0 frees the cache).  A matcher that is in a state it
+ * has been in before produces the same mask: with the cache that mask is not uploaded again. */
+int fns_b200_engine_mask_cache(fns_b200_engine * e, int slots);
+int fns_b200_engine_mask_stats(const fns_b200_engine * e, int64_t * hits, int64_t * misses, int64_t * bytes_uploaded);
+/* Engine::pick_async with the producer's tensor (one mask row, or one per logit row; NULL = unmasked).  Logits on the
+ * device, session histories on the device (fns_b200_engine_append).  mask_states_host NULL: the masks are staged and
+ * uploaded as in fns_b200_engine_pick_async.  Else mask_states_host[rows] names every row's grammar state (any 64-bit
+ * id the caller keeps per matcher state; FNS_B200_NO_MASK = this row is unmasked): a state the cache holds uploads
+ * nothing, a new one replaces the state that was not asked for longest.  All picks of an engine that use the cache
+ * must be issued on one stream (the uploads are ordered with the kernels that read the slots by that stream). */
+#define FNS_B200_NO_MASK 0xffffffffffffffffull
+int fns_b200_engine_pick_async_dl(fns_b200_engine * e, const void * logits, int dtype, int64_t row_stride, int rows,
+                                  const fns_b200_dl_tensor * masks, const uint64_t * mask_states_host,
+                                  const fns_b200_params * params_host, void * stream);
+/* ceil(vocab / 32): the words of one mask row of this engine (xgrammar::GetBitmaskSize, src/engine.cu:825). */
+int fns_b200_engine_words(const fns_b200_engine * e);
 /* Engine::pick_wait (src/engine.cu:849-852): waits for the oldest pick in flight; tokens_host[rows]. */
 int fns_b200_engine_pick_wait(fns_b200_engine * e, int32_t * tokens_host);
 /* Device copy of the tokens of the latest pick (the reference's io_ + 2), for a forward pass that is queued
@@ -241,6 +282,72 @@ int fns_b200_engine_verify(fns_b200_engine * e, const void * logits, int dtype, 
 /* Prompt-lookup draft (include/fns/lookup.h:12-27) on the host: the continuation of the latest earlier
  * occurrence of the final n-gram of the history, n = 4 down to 2.  Returns the number of ids written. */
 int fns_b200_lookup_draft(const int32_t * history_host, int n_history, int want, int32_t * out_host);
+
+/* The same draft for a batch of sessions on the device: history [rows][history_stride] with history_len[rows];
+ * out [rows][out_stride] receives at most `want` ids per row, out_n[rows] their count. */
+int fns_b200_lookup_draft_rows(const int32_t * history, int64_t history_stride, const int32_t * history_len, int rows,
+                               int want, int32_t * out, int64_t out_stride, int32_t * out_n, void * stream);
+
+/* ---- the speculation driver of fns-serve (tools/fns_serve/fns_serve.cpp:340-354, 410-519) ----------------------------
+ * Host code.  The grammar matcher and the model stay the caller's, behind callbacks. */
+typedef struct fns_b200_grammar {  /* xgrammar::GrammarMatcher as fns-serve drives it */
+    void * user;
+    void (*fill)(void * user, int32_t * mask_words);   /* FillNextTokenBitmask into ceil(vocab / 32) words */
+    int (*accept)(void * user, int32_t token);         /* AcceptToken: 0 = rejected */
+    int (*terminated)(void * user);                    /* IsTerminated; may be NULL */
+    void (*rollback)(void * user, int tokens);         /* Rollback */
+} fns_b200_grammar;
+/* Masks for the columns of a window (fns_serve.cpp:340-354): column c's mask follows the committed prefix plus
+ * draft[0 .. c).  wmask [(nd + 1)][words].  Returns the number of usable columns W (a draft id the grammar rejects
+ * cuts the window) and leaves the matcher at the committed prefix; without a grammar (g NULL) W = nd + 1. */
+int fns_b200_spec_window_masks(const fns_b200_grammar * g, const int32_t * draft, int nd, int words, uint32_t * wmask);
+
+typedef struct fns_b200_spec_counters {  /* the counters of fns-serve's "done" line (fns_serve.cpp:523-532) */
+    int32_t generated, windows, drafted, accepted, emitted, skipped, iterations;
+} fns_b200_spec_counters;
+/* The accept / commit loop over one verified window (fns_serve.cpp:486-508): out[W] are the columns' choices; the
+ * choice of column c is committed while every earlier column matched its draft.  committed[W] receives the tokens to
+ * emit, *engaged their number (what Engine::presence_commit takes).  Returns 0 = go on, 1 = a stop token was
+ * committed, 2 = max_tokens reached, negative = argument error / token rejected by the grammar. */
+int fns_b200_spec_commit(const int32_t * out, int W, const int32_t * draft, int nd, const int32_t * stop, int n_stop,
+                         int max_tokens, const fns_b200_grammar * g, fns_b200_spec_counters * c, int32_t * committed,
+                         int * engaged, int * window_accepted, int * window_offered);
+
+/* Adaptive window width (fns_serve.cpp:430-459): from the acceptance rate of this request and the measured cost of
+ * windows of each width, the number of draft ids that maximises expected tokens per unit of time (0 = do not
+ * speculate this step).  Costs are exponentially weighted means of wall-clock seconds and persist across requests. */
+typedef struct fns_b200_spec_policy {
+    int32_t spec;                /* widest window (columns) */
+    int32_t skipped_proposals;
+    uint64_t accepted, offered;  /* of this request */
+    double cost[FNS_B200_MAX_WINDOW + 1];  /* cost[w]: a window of w columns; cost[1]: an ordinary step; 0 = unknown */
+} fns_b200_spec_policy;
+void fns_b200_spec_policy_init(fns_b200_spec_policy * p, int spec);
+void fns_b200_spec_policy_new_request(fns_b200_spec_policy * p);
+int fns_b200_spec_choose_width(fns_b200_spec_policy * p, int nd_max);
+void fns_b200_spec_observe(fns_b200_spec_policy * p, int width, double elapsed_s, int window_accepted, int window_offered);
+
+/* The model behind the sampler: logits of W columns, column c after ids[0 .. c] at positions p0 .. p0 + c
+ * (Engine::prefill / step_logits / verify's forward pass).  *logits: device [W][*row_stride]. */
+typedef struct fns_b200_model {
+    void * user;
+    int (*forward)(void * user, const int32_t * ids, int W, int p0, const void ** logits, int64_t * row_stride);
+} fns_b200_model;
+/* The decode loop of fns-serve for one request (fns_serve.cpp:383-521): sequential when spec <= 1, else
+ * speculative with prompt-lookup drafts of up to spec - 1 ids, verification windows (fns_b200_engine_verify), the
+ * accept rule and presence_commit.  Column c draws with Philox counter (generated-token index), so both modes give
+ * the same tokens for the same seed.  e: an engine for one session with max_rows >= spec (and max_history >=
+ * max_tokens when a penalty is set).  out_tokens[max_tokens]; counters->generated is their number. */
+int fns_b200_spec_decode(fns_b200_engine * e, const fns_b200_model * m, const fns_b200_grammar * g, const int32_t * prompt,
+                         int n_prompt, int max_tokens, const int32_t * stop, int n_stop, const fns_b200_params * sp, int dtype,
+                         int spec, fns_b200_spec_policy * policy, int32_t * out_tokens, fns_b200_spec_counters * counters,
+                         void * stream);
+
+/* The sampling fields of one request line of fns-serve (fns_serve.cpp:291-303, defaults serve/fns_server.py:387-395):
+ * "temperature" (0 = greedy), "top_p" (1), "top_k" (0 = k_cap), "seed" (0), "presence_penalty" (0), and this
+ * library's "min_p" (0), "repetition_penalty" (1), "frequency_penalty" (0).  A missing or non-numeric field keeps
+ * its default; counter is set to 0 (the caller counts generated tokens). */
+int fns_b200_params_from_json(const char * json_line, fns_b200_params * out);
 
 /* ---- multi-GPU dispatcher ---------------------------------------------------------------------------------------
  * No counterpart in the reference, which is single-GPU and samples one row per call (docs/ENGINE.md:132).  One
