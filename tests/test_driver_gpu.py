@@ -176,3 +176,37 @@ def test_speculative_decoding_under_a_grammar(dev):
         assert ok
         runs.append(tokens)
     assert runs[0] == runs[1] and len(runs[0]) == 30
+
+
+def test_json_lines_service_answers_like_the_oracle(dev, oracle, tmp_path):
+    """The request surface (tools/fns_serve/fns_serve.cpp:291-303) end to end: defaults = greedy, the five fields reach
+    the sampler, `draw` is the Philox counter, a bad line gives an error line and the service goes on."""
+    import io
+    import json
+
+    from flintnsteel_b200.serve import serve
+
+    w = wl.session_batch(seed=71, rows=2, vocab=3000, history=8)
+    np.save(tmp_path / "rows.npy", w.logits)
+    allowed = [int(i) for i in np.nonzero(np.unpackbits(w.masks[0].view(np.uint8), bitorder="little")[:3000])[0]]
+    lines = [
+        json.dumps({"id": 1, "logits": w.logits[0].tolist()}),
+        json.dumps({"id": 2, "logits_npy": str(tmp_path / "rows.npy"), "temperature": 0.9, "top_p": 0.9, "top_k": 30,
+                    "seed": 11, "presence_penalty": 0.7, "history": [5, 9, 5], "allowed": allowed, "draw": 4}),
+        "this is not json",
+        json.dumps({"id": 3, "logits": [0.0, 1.0], "allowed": [7]}),
+        json.dumps({"id": 4, "logits": [0.0, 3.0, 1.0]}),
+    ]
+    out = io.StringIO()
+    serve(io.StringIO("\n".join(lines) + "\n"), out)
+    replies = [json.loads(x) for x in out.getvalue().splitlines()]
+    assert len(replies) == 5
+    assert replies[0] == {"id": 1, "tokens": [int(w.logits[0].argmax())]}
+    p = make_params(2, temperature=0.9, top_p=0.9, top_k=30, seed=11, presence=0.7)
+    p["counter"] = [4, 5]
+    masks = np.repeat(w.masks[:1], 2, axis=0)
+    hist = np.array([[5, 9, 5], [5, 9, 5]], np.int32)
+    want, _ = oracle.sample_rows(w.logits, p, 64, masks, hist, np.array([3, 3], np.int32))
+    assert replies[1] == {"id": 2, "tokens": want.tolist()}
+    assert "error" in replies[2] and "error" in replies[3] and "vocabulary" in replies[3]["error"]
+    assert replies[4] == {"id": 4, "tokens": [1]}
