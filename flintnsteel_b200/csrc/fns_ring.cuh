@@ -224,14 +224,6 @@ __device__ void block_sort_desc(uint64_t * a, int m) {
 }
 
 
-#ifdef FNS_RING_TIMING
-__device__ unsigned g_ring_t[1024][16];
-#define RT(i) if (threadIdx.x == 0 && blockIdx.x < 1024) g_ring_t[blockIdx.x][i] = (unsigned) (clock64() - rt0);
-#define RT0 const long long rt0 = clock64();
-#else
-#define RT(i)
-#define RT0
-#endif
 
 constexpr int kRegOwn = 4;  // owned history ids that a thread keeps in registers (4 * 512 per row)
 
@@ -312,7 +304,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const uint32_t * mrow = a.masks ? a.masks + (size_t) (a.mask_rows ? a.mask_rows[row] : row) * a.mask_stride : nullptr;
-    RT0
     // without a mask every chunk is wanted: the first stages start now
     if (tid == 0 && !mrow)
         for (int u = 0; u < depth && u < n_stages; ++u) issue_stage(u, u, 0xffffu);
@@ -431,7 +422,8 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                 mine[u] = false;
                 if (offs[u] < (uint32_t) V && ids[u] >= a.id_base) {
                     const uint32_t bit = 1u << (offs[u] & 31);
-                    if (*(volatile uint32_t *) &eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
+                    // (a plain read first: a stale 1 is settled by the atomic itself, and a 0 stays 0)
+                    if (eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
                 }
                 const uint32_t b = __ballot_sync(kFull, mine[u]);
                 pre[u] = total + (uint32_t) __popc(b & below);
@@ -469,7 +461,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         my_val[r] = 0u;
     }
 
-    RT(0)
     // 3. The streaming pass.
     float tmax = -INFINITY;     // this thread's maximum so far
     uint64_t best = 0ull;       // k == 1: this thread's best key
@@ -594,7 +585,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     if (gave_up && a.err) atomicExch(a.err, 3);  // a copy never arrived: the result of this row is not valid
     __syncthreads();  // the ring is free: what follows lives there
-    RT(1)
 
     uint64_t * buf = reinterpret_cast<uint64_t *>(ring);
     uint64_t * sel = buf + a.cap;
@@ -628,7 +618,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         thr_v += 0.0f;
     }
     uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
-    RT(2)
 
     // 5. The candidates.
     auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add
@@ -663,7 +652,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     copy_word_wait();
     __syncthreads();
-    RT(3)
     for (int attempt = 0; attempt < 2; ++attempt) {
         const bool careful = attempt == 1;
         // (a) the ragged end
@@ -782,7 +770,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                 }
             }
         }
-        RT(4)
         // (c) the listed cells, one vector per thread and round, read again.  The careful way walks every cell
         // instead, a round of NT cells at a time, with a vote after each round.
         bool listed = true;
@@ -899,7 +886,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         __syncthreads();
     }
 
-    RT(5)
     // 6. The best k in the total order, and the draw.
     p.counter += (uint64_t) col;  // column c of a window draws with counter + c (src/engine.cu:756)
     int32_t * tok = a.out_tokens ? a.out_tokens + row : nullptr;
@@ -954,11 +940,9 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
             for (int e = 0; e < 4; ++e) buf[4 * r + e] = q[e];
         }
         __syncthreads();
-        RT(6)
         int keep = 4;  // a merged run keeps the best `keep` keys: the power of two that holds k
         while (keep < k) keep <<= 1;
         const uint64_t * res = merge_runs_pow2<NT>(buf, buf + half, runs, 2, keep);
-        RT(7)
         got = n < k ? n : k;
         for (int i = tid; i < got; i += NT) sorted[i] = res[i];
     } else {
@@ -977,12 +961,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     }
     for (int j = got + tid; j < a.k_cap; j += NT) sorted[j] = 0ull;
     __syncthreads();
-    RT(8)
-#ifdef FNS_RING_TIMING
-    if (tid == 0 && blockIdx.x < 1024) g_ring_t[blockIdx.x][15] = (unsigned) n;
-#endif
     draw_tail<NT>(sorted, got, pj, acc, reinterpret_cast<double *>(sel), sh.sc, p, a.k_cap, tok, oc);
-    RT(9)
 }
 
 }  // namespace fnsb

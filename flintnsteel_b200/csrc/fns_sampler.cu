@@ -75,6 +75,7 @@ struct SelectArgs {
     int ring_depth;  // k_ring: stages of shared memory that the copies rotate through
     int ring_off;    // k_ring: where the ring starts in the block's shared memory
     int own_off;     // k_ring: where the list of owned history ids starts
+    int hist_cap;    // k_cluster: history ids per row that are staged in shared memory (a multiple of 4)
     uint64_t * cand;  // [rows][slices][k_cap] sorted keys, 0 = empty
     unsigned * tickets;         // [rows], zero between launches
     int32_t * out_tokens;       // [rows], may be null
@@ -760,7 +761,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
                 if (offs[u] < (uint32_t) n_s && ids[u] >= a.id_base) {
                     const uint32_t bit = 1u << (offs[u] & 31);
                     // (the plain read first: excluded ids and repeats, the common case under a mask, cost no atomic)
-                    if (*(volatile uint32_t *) &eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
+                    if (eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;  // (a stale 1 is settled by the atomic)
                 }
                 const uint32_t b = __ballot_sync(kFull, mine[u]);
                 pre[u] = total + (uint32_t) __popc(b & below);
@@ -1352,6 +1353,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) k_select(const SelectArgs a) {
 }  // namespace fnsb
 
 #include "fns_ring.cuh"
+#include "fns_cluster.cuh"
 
 namespace fnsb {
 
@@ -1467,6 +1469,7 @@ struct fns_b200_sampler {
     int force_slices;
     int force_threads;
     bool logits_in_host_memory;  // the next call's logits are page-locked host memory (set by the engine glue)
+    bool cluster_ok;             // a cluster of 16 CTAs of k_cluster can be resident on this device
     uint64_t * cand;   // [rows][slices][k_cap] sorted keys of the slices
     size_t cand_entries;
     unsigned * tickets;  // [max_rows], zero between launches
@@ -1483,8 +1486,9 @@ namespace {
 struct Plan {
     int threads, slices, slice_len, cap, trigger, own_cap, vec, list_cap, seg_cap;
     size_t smem_select;
+    bool cluster; // k_cluster (one to four rows)
     bool ring;    // k_ring instead of k_select
-    int n_stages, ring_depth, ring_off, own_off;
+    int n_stages, ring_depth, ring_off, own_off, hist_cap;
 };
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -1586,6 +1590,29 @@ bool make_ring_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, 
     return true;
 }
 
+// k_cluster: one cluster of 16 CTAs per row for calls of one to four rows.
+bool make_cluster_plan(const fns_b200_sampler * s, int dtype, int vocab, int hist_bound, Plan & pl) {
+    const int k_cap = s->k_cap;
+    const size_t esz = dtype == FNS_B200_BF16 ? 2 : 4;
+    if (k_cap > kClusterMaxK || !s->cluster_ok) return false;
+    pl.cluster = true;
+    pl.ring = false;
+    pl.threads = kClusterThreads;
+    pl.slices = kClusterCtas;
+    pl.slice_len = round_up((vocab + kClusterCtas - 1) / kClusterCtas, 128);
+    pl.vec = (int) (16 / esz);
+    pl.cap = kClusterBuf;
+    pl.trigger = kClusterLocal / 2;
+    pl.own_cap = hist_bound > 0 ? round_up(hist_bound < pl.slice_len ? hist_bound : pl.slice_len, 4) : 0;
+    pl.list_cap = 0;
+    pl.seg_cap = 0;
+    const size_t cs_bytes = (sizeof(ClusterShared) + 127) & ~(size_t) 127;
+    pl.smem_select = cs_bytes + (size_t) pl.slice_len / 8 + (size_t) pl.slice_len * esz + (size_t) (hist_bound + 4) * 4 + (size_t) pl.own_cap * 4 +
+                     (size_t) kClusterThreads * 2 * 8 + (size_t) (kClusterLocal + k_cap) * 8 + (size_t) (kClusterBuf + k_cap) * 8 +
+                     (size_t) k_cap * 8 * 3;
+    return pl.smem_select <= 112 * 1024;  // sixteen of them must be resident together (two fit an SM)
+}
+
 // Whole rows (from five rows on) go to k_ring when the call has no mask - every byte of the rows has to move, and
 // the copy engine moves it best - and whenever k_cap exceeds the 512 thread maxima that k_select's bound is made of.
 // Masked calls with k_cap <= 512 stay with k_select: its per-vector skipping and its loads in registers serve a
@@ -1593,6 +1620,11 @@ bool make_ring_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, 
 bool make_plan(const fns_b200_sampler * s, int dtype, int vocab, int rows, int hist_bound, bool aligned, bool masked, Plan & pl) {
     const bool whole_rows = s->force_threads <= 0 && s->force_slices <= 0 && rows > 4;
     pl.ring = false;
+    pl.cluster = false;
+    if (s->force_threads <= 0 && s->force_slices <= 0 && rows <= 4 && aligned && !s->logits_in_host_memory &&
+        make_cluster_plan(s, dtype, vocab, hist_bound, pl))
+        return true;
+    pl.cluster = false;
     if (whole_rows && aligned && !s->logits_in_host_memory && (!masked || s->k_cap > kRingThreads) &&
         make_ring_plan(s, dtype, vocab, rows, hist_bound, pl))
         return true;
@@ -1645,6 +1677,10 @@ cudaError_t configure_kernels_once() {  // call with the device current
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_ring<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_ring<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = opt_in(k_finalize, 200 * 1024);
+    if (e == cudaSuccess) e = opt_in(k_cluster<float>, 112 * 1024);
+    if (e == cudaSuccess) e = opt_in(k_cluster<__nv_bfloat16>, 112 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_cluster<float>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_cluster<__nv_bfloat16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e == cudaSuccess) configured[dev] = true;
     return e;
 }
@@ -1710,6 +1746,49 @@ cudaError_t launch_ring_t(const SelectArgs & a, int rows, size_t smem, cudaStrea
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+template <typename T>
+cudaError_t launch_cluster_t(const SelectArgs & a, int rows, size_t smem, cudaStream_t st) {
+    const cudaError_t ce = configure_kernels_once();
+    if (ce != cudaSuccess) return ce;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kClusterCtas, (unsigned) rows);
+    cfg.blockDim = dim3(kClusterThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kClusterCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the prologue overlaps the previous kernel's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, k_cluster<T>, a);
+}
+
+// Whether sixteen CTAs of k_cluster with their largest shared-memory request fit the device as one cluster.
+bool cluster_fits_device() {
+    if (configure_kernels_once() != cudaSuccess) return false;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kClusterCtas, 1);
+    cfg.blockDim = dim3(kClusterThreads);
+    cfg.dynamicSmemBytes = 112 * 1024;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kClusterCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, k_cluster<float>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return n >= 4;  // four rows at once
+}
+
 cudaError_t launch_final(const FinalArgs & a, int rows, cudaStream_t st) {
     const size_t smem = final_smem(a.lists, a.list_len, a.k_cap);
     const cudaError_t ce = configure_kernels_once();
@@ -1753,7 +1832,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     const bool aligned = ((uintptr_t) logits % 16 == 0) && ((size_t) row_stride * esz % 16 == 0 || rows == 1);
     const int hist_bound = (history ? (int) history_stride : 0) + n_draft;
     if (!make_plan(s, dtype, vocab, rows, hist_bound, aligned, masks != nullptr, pl)) return fail(s, FNS_B200_ERR_CAPACITY, "no launch plan fits (vocab too large for k_cap)");
-    if ((size_t) rows * pl.slices * s->k_cap > s->cand_entries) return fail(s, FNS_B200_ERR_CAPACITY, "workspace too small for this call");
+    if (!pl.cluster && (size_t) rows * pl.slices * s->k_cap > s->cand_entries) return fail(s, FNS_B200_ERR_CAPACITY, "workspace too small for this call");
     SelectArgs a{};
     a.logits = logits;
     a.row_stride = row_stride;
@@ -1781,6 +1860,7 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     a.ring_depth = pl.ring_depth;
     a.ring_off = pl.ring_off;
     a.own_off = pl.own_off;
+    a.hist_cap = pl.cluster ? (int) ((history ? history_stride : 0) / 4 * 4) : 0;
     a.cand = s->cand;
     a.tickets = s->tickets;
     a.out_tokens = out_tokens;
@@ -1789,7 +1869,9 @@ int run_select(fns_b200_sampler * s, const void * logits, int dtype, int64_t row
     const bool prof = s->prof_on && (size_t) (s->prof_calls + 1) * 3 <= s->prof_ev.size();
     if (prof) cudaEventRecord(s->prof_ev[(size_t) s->prof_calls * 3], st);
     cudaError_t e;
-    if (!pl.ring) e = launch_select(a, pl.threads, dtype, pl.vec, rows, pl.smem_select, st);
+    if (pl.cluster) e = dtype == FNS_B200_BF16 ? launch_cluster_t<__nv_bfloat16>(a, rows, pl.smem_select, st)
+                                               : launch_cluster_t<float>(a, rows, pl.smem_select, st);
+    else if (!pl.ring) e = launch_select(a, pl.threads, dtype, pl.vec, rows, pl.smem_select, st);
     else if (dtype == FNS_B200_BF16) e = launch_ring_t<__nv_bfloat16>(a, rows, pl.smem_select, st);
     else e = launch_ring_t<float>(a, rows, pl.smem_select, st);
     if (e != cudaSuccess) return fail_cuda(s, e, "select launch");
@@ -1838,6 +1920,7 @@ int fns_b200_create(int device, int max_rows, int max_vocab, int k_cap, int max_
         delete s;
         return FNS_B200_ERR_CUDA;
     }
+    s->cluster_ok = cluster_fits_device();
     // Candidate workspace: the largest rows * slices any plan can produce, bounded by the merge limit.
     int max_slices = kMaxMergeKeys / k_cap;
     if (max_slices > kMaxSlices) max_slices = kMaxSlices;
@@ -1919,13 +2002,6 @@ int fns_b200_device_status(fns_b200_sampler * s, void * stream) {
     return FNS_B200_OK;
 }
 
-#ifdef FNS_RING_TIMING
-int fns_b200_debug_ring_times(unsigned * out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, fnsb::g_ring_t, sizeof(unsigned) * 1024 * 16);
-    return 0;
-}
-#endif
 
 int fns_b200_hint_host_logits(fns_b200_sampler * s, int on) {
     if (!s) return FNS_B200_ERR_ARG;

@@ -161,3 +161,37 @@ def test_compat_shim_grows_its_workspace(dev, library_path):
     argmax(small.data_ptr(), 1000, out[2:3].data_ptr(), st, None)
     torch.cuda.synchronize()
     assert out.tolist() == [123, 299_999, 123]
+
+
+def test_calls_can_be_captured_in_a_cuda_graph(dev, oracle):
+    """The sampler is stream-ordered with no host synchronisation and no set-up left in the call path after
+    fns_b200_create, so a call can be captured and replayed: one row (sliced plan, tickets in the workspace), a
+    whole-row masked batch (k_select) and an unmasked batch (k_ring, bulk copies), each against its eager run."""
+    from flintnsteel_b200.sampler import Sampler, params_to_device
+
+    cases = [wl.grammar_row(seed=3), wl.session_batch(seed=5, rows=9, vocab=40_000, history=128),
+             wl.session_batch(seed=6, rows=9, vocab=40_000, history=128)]
+    cases[2].masks = None
+    for w in cases:
+        s = Sampler(0, max_rows=w.rows, max_vocab=w.vocab, k_cap=64, max_history=4096)
+        lg = torch.from_numpy(w.logits).to(dev)
+        masks = None if w.masks is None else torch.from_numpy(w.masks.view(np.int32)).to(dev)
+        hist, hl = torch.from_numpy(w.history).to(dev), torch.from_numpy(w.history_len).to(dev)
+        pd = params_to_device(w.params, dev)
+        eager = torch.empty(w.rows, dtype=torch.int32, device=dev)
+        s.sample_rows(lg, pd, eager, masks=masks, history=hist, history_len=hl)
+        torch.cuda.synchronize()
+        out = torch.full((w.rows,), -5, dtype=torch.int32, device=dev)
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(3):  # back-to-back launches inside one graph (programmatic dependent launch edges)
+                    s.sample_rows(lg, pd, out, masks=masks, history=hist, history_len=hl)
+        for _ in range(2):
+            out.fill_(-5)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, eager)
+        s.device_status()
+        s.close()

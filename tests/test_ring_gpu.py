@@ -124,3 +124,65 @@ def test_special_values_in_whole_rows(dev, oracle):
     tokens, cands = run_rows(w, dev)
     assert list(tokens[:5]) == [100_000, 150_077, 90_005, 0, -1]
     check_against_oracle(oracle, w, tokens, cands)
+
+
+# ---- one to four rows: the cluster kernel (16 CTAs per row, candidates meet in distributed shared memory) -----------
+@pytest.mark.parametrize("n", [1, 33, 127, 2048, 2049, 20_000, 151_936, 262_144])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_few_rows_of_any_length(dev, oracle, n, bf16):
+    """Slices that are empty, partly filled, ragged at the end; masks, histories with repeats; k_cap 64 and 128."""
+    g = wl.rng(7000 + n)
+    for rows, k_cap in ((1, 64), (3, 128), (4, 64)):
+        x = g.standard_normal((rows, n), dtype=np.float32) * np.float32(2.5)
+        masks = np.stack([wl.random_mask(g, n, d) for d in (0.6, 1.0, 0.02, 0.3)[:rows]])
+        hist = g.integers(-2, n + 2, size=(rows, 300), dtype=np.int32)
+        hist[0, :50] = hist[0, 0]
+        p = make_params(rows, temperature=0.9, top_k=0, top_p=0.95, min_p=0.01, repetition=1.2, presence=0.3, frequency=0.2, seed=n)
+        p["temperature"][rows - 1] = 0.0
+        logits = wl.f32_to_bf16_bits(x) if bf16 else x
+        w = wl.Workload("few", logits, p, masks, hist, np.array([300, 0, 7, 300][:rows], np.int32), bf16=bf16, k_cap=k_cap)
+        check_against_oracle(oracle, w, *run_rows(w, dev, max_history=300))
+
+
+def test_few_rows_with_equal_values_and_hot_histories(dev, oracle):
+    """Rows of one value overflow every CTA's region, so every CTA reduces its slice to its own best k and the lists are
+    merged; a history that holds the row's largest logits many times exercises the occurrence count."""
+    n = 151_936
+    g = wl.rng(99)
+    x = np.empty((4, n), np.float32)
+    x[0] = 1.25
+    x[1] = np.repeat(np.arange(n // 512 + 1, dtype=np.float32), 512)[:n]
+    x[2:] = wl.gaussian_logits(g, 2, n, 2.5)
+    top = np.argsort(-x[2])[:200].astype(np.int32)
+    hist = np.zeros((4, 4096), np.int32)
+    hist[:] = np.tile(np.arange(4096, dtype=np.int32) * 37 % n, (4, 1))
+    hist[2, :2000] = np.repeat(top, 10)
+    hist[3, :3000] = np.tile(top[:30], 100)
+    hl = np.array([4096, 0, 4096, 4096], np.int32)
+    for temperature in (0.0, 0.8):
+        p = make_params(4, temperature=temperature, top_k=64, top_p=0.98, repetition=1.15, presence=0.5, frequency=0.25, seed=4)
+        p["frequency"][3] = -0.05  # more occurrences raise the value: every owned id needs its count
+        w = wl.Workload("few_equal", x, p, None, hist, hl)
+        check_against_oracle(oracle, w, *run_rows(w, dev))
+
+
+def test_one_verification_window_of_four_columns(dev, oracle):
+    """Engine::verify's shape (src/engine.cu:745-757): one window, three draft ids, masks per column, history."""
+    sw = wl.spec_windows(seed=31, windows=1, n_draft=3, temperature=0.85)
+    sw.params["presence"], sw.params["top_k"] = 0.9, 30
+    g = wl.rng(32)
+    masks = np.stack([wl.random_mask(g, sw.vocab, 0.5) for _ in range(4)])
+    hist = g.integers(0, sw.vocab, size=(1, 64), dtype=np.int32)
+    from flintnsteel_b200.sampler import Sampler, params_to_device
+
+    s = Sampler(0, max_rows=4, max_vocab=sw.vocab, k_cap=64, max_history=64)
+    toks = torch.empty(4, dtype=torch.int32, device=dev)
+    acc = torch.empty(1, dtype=torch.int32, device=dev)
+    s.verify_accept(torch.from_numpy(sw.logits).to(dev), torch.from_numpy(sw.draft).to(dev), params_to_device(sw.params, dev),
+                    toks, acc, masks=torch.from_numpy(masks.view(np.int32)).to(dev), history=torch.from_numpy(hist).to(dev),
+                    history_len=torch.tensor([64], dtype=torch.int32, device=dev))
+    torch.cuda.synchronize()
+    s.device_status()
+    et, ea = oracle.verify_window(sw.logits, sw.draft[0], sw.params, masks=masks, hist=hist[0])
+    assert np.array_equal(toks.cpu().numpy(), et) and acc.item() == ea
+    s.close()
