@@ -145,27 +145,41 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_region(fn, steps):
+        """Exactly `steps` calls of fn(i), device time, bracketed by barrier + synchronise, max over ranks."""
+        for i in range(3):  # re-warm right before the clock starts: nothing idles between warm-up and the region
+            fn(i)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for i in range(steps):
+            fn(i)
+        b.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for i in range(W):
         step(i)
     barrier()
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
-        time.sleep(0.25)
-    # ---- timed region: exactly K steps, device time, max over ranks ----------------------------------------
+    # ---- timed regions: exactly K steps each, repeated; the median region is the value ----------------------
     launches0 = sampler.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(K):
-        step(i)
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    launches = sampler.launch_count() - launches0
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    total_ms = float(ms.item())
+    regions = [timed_region(step, K) for _ in range(args.repeats)]
+    launches = (sampler.launch_count() - launches0) * K // (args.repeats * (K + 3))
+    total_ms = float(np.median(regions))
+    if args.only_headline:  # profiler runs: the timed regions and nothing else
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": world * rows * K / (total_ms / 1e3), "unit": "rows/s",
+                              "ms_per_step": total_ms / K, "config": {"workload": WORKLOAD + ("_all_ids_allowed" if args.no_masks else "")},
+                              "note": "--only-headline: a profiler run, not a benchmark line"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     # a longer untimed stretch of the same steps so that the clock record has samples under load
     if rank == 0:
         t_end = time.time() + 1.0
@@ -191,35 +205,67 @@ def run_b200(args):
     sel_ms, fin_ms, calls = sampler.profile_end()
     isolated_us = sel_ms / max(calls, 1) * 1e3
     # the same rows with every id allowed: no vector can be skipped, so every logit byte comes from HBM
-    for i in range(3):
-        step(i, masked=False)
-    torch.cuda.synchronize()
-    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    d0.record()
-    for i in range(K):
-        step(i, masked=False)
-    d1.record()
-    torch.cuda.synchronize()
-    dense_s = d0.elapsed_time(d1) / K / 1e3
+    dense_regions = [timed_region(lambda i: step(i, masked=False), K) for _ in range(max(3, args.repeats // 3))]
+    dense_s = float(np.median(dense_regions)) / K / 1e3
     dense_bytes = rows * (host[0].row_bytes() - 4 * host[0].masks.shape[1])
+    # the same densities with the allowed ids scattered instead of in 20 runs: nearly every 16-byte vector holds one
+    scat = []
+    for b, w in enumerate(host):
+        g = wl.rng(77 + b)
+        m = np.stack([wl.random_mask(g, vocab, float(f)) for f in w.meta["allowed_fraction"]])
+        scat.append(torch.from_numpy(m.view(np.int32)).to(dev))
+
+    def step_scattered(i):
+        d = dev_in[i % len(dev_in)]
+        sampler.sample_rows(d["logits"], d["params"], out, masks=scat[i % len(scat)], history=d["history"], history_len=d["history_len"])
+
+    scat_s = float(np.median([timed_region(step_scattered, K) for _ in range(3)])) / K / 1e3
+    del scat
+    # strong scaling of the same fixed batch: 256 rows in all, rows / world per rank
+    strong = None
+    if world > 1:
+        share = max(1, rows // world)
+        lo = (rank * share) % rows
+
+        def step_strong(i):
+            d = dev_in[i % len(dev_in)]
+            sampler.sample_rows(d["logits"][lo:lo + share], d["params"][lo * 48:(lo + share) * 48], out[:share],
+                                masks=d["masks"][lo:lo + share], history=d["history"][lo:lo + share],
+                                history_len=d["history_len"][lo:lo + share])
+
+        strong_ms = float(np.median([timed_region(step_strong, K) for _ in range(3)]))
+        strong = {"rows_total": share * world, "rows_per_gpu": share, "ms_per_step": strong_ms / K,
+                  "rows_per_s": share * world * K / (strong_ms / 1e3),
+                  "note": "the fixed 256-row batch split over the GPUs (strong scaling) next to the weak figure above"}
 
     # ---- end to end through the engine glue: host buffers in, tokens out to the host, every step -----------
     eng = Engine(local, max_rows=rows, vocab=vocab, k_cap=64, max_history=host[0].history.shape[1])
     host_pin = [dict(logits=pinned(w.logits), masks=pinned(w.masks.view(np.int32)), history=pinned(w.history),
                      history_len=pinned(w.history_len), params=pinned(w.params.view(np.uint8))) for w in host[:2]]
 
-    def e2e(steps, logits_on_host):
+    def e2e(steps, logits_on_host, history_on_device=False, cached_masks=False):
+        """Steps through the engine glue with host inputs: step i + 1 is queued (pick_async) before the host waits for
+        step i (pick_wait), as the reference chains its decode (src/engine.cu:796-852); two slots alternate."""
+        def queue(i):
+            h, d = host_pin[i % 2], dev_in[i % 2]
+            if cached_masks:
+                eng.pick_async_dl(d["logits"], h["params"], masks=h["masks"], mask_states=states[i % 2])
+            else:
+                eng.pick_async(h["logits"] if logits_on_host else d["logits"], h["params"], masks_host=h["masks"],
+                               history_host=None if history_on_device else h["history"],
+                               history_len_host=None if history_on_device else h["history_len"],
+                               logits_on_host=logits_on_host, host_stable=True)
         for warm in range(2):
-            h, d = host_pin[warm % 2], dev_in[warm % 2]
-            eng.pick(h["logits"] if logits_on_host else d["logits"], h["params"], masks_host=h["masks"],
-                     history_host=h["history"], history_len_host=h["history_len"], logits_on_host=logits_on_host, host_stable=True)
+            queue(warm)
+            eng.pick_wait(rows)
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
+        queue(0)
         for i in range(steps):
-            h, d = host_pin[i % 2], dev_in[i % 2]
-            eng.pick(h["logits"] if logits_on_host else d["logits"], h["params"], masks_host=h["masks"],
-                     history_host=h["history"], history_len_host=h["history_len"], logits_on_host=logits_on_host, host_stable=True)
+            if i + 1 < steps:
+                queue(i + 1)
+            eng.pick_wait(rows)
         b.record()
         barrier()
         t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
@@ -235,6 +281,21 @@ def run_b200(args):
     e2e_steps = max(3, min(K, 20))
     e2e_host = e2e(e2e_steps, True)
     e2e_engine = e2e(max(3, min(K, 100)), False)
+    # the sessions' histories kept on the device (fns_b200_engine_append), masks from the host: what a decode step uploads
+    for b in range(1):
+        hd = dev_in[0]["history"]
+        eng.reset()
+        for c in range(0, hd.shape[1], 64):  # the committed tokens so far, 64 columns at a time
+            cols = hd[:, c:c + 64].contiguous()
+            counts = np.full(rows, cols.shape[1], np.int32)
+            eng.append(cols.data_ptr(), cols.shape[1], rows, counts_host=counts)
+        torch.cuda.synchronize()
+    e2e_engine_dev_hist = e2e(max(3, min(K, 100)), False, history_on_device=True)
+    # ... and the masks kept on the device by grammar state: a state seen before uploads nothing
+    eng.mask_cache(2 * rows)
+    states = [np.arange(rows, dtype=np.uint64) + np.uint64(1000 * b) for b in range(2)]
+    e2e_engine_cached = e2e(max(3, min(K, 100)), False, history_on_device=True, cached_masks=True)
+    hits, misses, up_bytes = eng.mask_stats()
 
     result = {
         "metric": METRIC, "value": world * rows * K / (total_ms / 1e3), "unit": "rows/s", "n_gpus": world,
@@ -254,10 +315,20 @@ def run_b200(args):
                      (NCU_TRAFFIC_BYTES if rows == 256 and not args.no_masks else None),
                      "traffic_note": "ncu dram bytes per launch of the capture summarised under profiles/; below the "
                                      "algorithmic bytes because vectors with no allowed id are never loaded",
-                     "all_ids_allowed": {"avg_launch_us": dense_s * 1e6, "bytes_per_launch": dense_bytes,
+                     "bound_note": "frac is algorithmic (dense) bytes over time, as the metric is defined; with this "
+                                   "workload's run-structured masks the kernel moves only `traffic` bytes and is "
+                                   "latency-bound, not HBM-bound: the HBM-bound figure is all_ids_allowed",
+                     "frac_of_traffic": (NCU_TRAFFIC_BYTES / sel_avg_s / 1e9 / peak) if rows == 256 and not args.no_masks else None,
+                     "all_ids_allowed": {"kernel": "k_ring", "avg_launch_us": dense_s * 1e6, "bytes_per_launch": dense_bytes,
                                          "achieved": dense_bytes / dense_s / 1e9 if dense_s > 0 else 0.0,
                                          "frac": dense_bytes / dense_s / 1e9 / peak if dense_s > 0 else 0.0,
-                                         "traffic": NCU_TRAFFIC_BYTES_DENSE if rows == 256 else None}},
+                                         "traffic": NCU_TRAFFIC_BYTES_DENSE if rows == 256 else None},
+                     "scattered_masks": {"avg_launch_us": scat_s * 1e6, "bytes_per_launch": rows * row_bytes,
+                                         "achieved": rows * row_bytes / scat_s / 1e9, "frac": rows * row_bytes / scat_s / 1e9 / peak,
+                                         "note": "the same per-row densities with random bits instead of 20 runs"}},
+        "value_stats": {"regions": len(regions), "ms_per_step_min": min(regions) / K, "ms_per_step_median": total_ms / K,
+                        "ms_per_step_max": max(regions) / K},
+        "strong256": strong,
         "e2e": {"value": e2e_host, "unit": "rows/s", "h2d_bytes_per_step": int(crossing + side_bytes),
                 "d2h_bytes_per_step": rows * 4, "steps": e2e_steps,
                 "host_input_bytes_per_step": int(rows * vocab * 4 + side_bytes),
@@ -268,12 +339,22 @@ def run_b200(args):
         "e2e_engine": {"value": e2e_engine, "unit": "rows/s", "h2d_bytes_per_step": int(side_bytes),
                        "d2h_bytes_per_step": rows * 4,
                        "note": "as the reference's Engine::pick_async is used: logits already on the GPU (the LM "
-                               "head wrote them), masks / histories / parameters from host memory, tokens back"},
+                               "head wrote them), masks / histories / parameters from host memory, tokens back",
+                       "device_histories": {"value": e2e_engine_dev_hist, "unit": "rows/s",
+                                            "h2d_bytes_per_step": int(rows * (host[0].masks.shape[1] * 4 + 48)),
+                                            "note": "session histories kept on the device (fns_b200_engine_append): a step "
+                                                    "uploads masks and parameters only"},
+                       "device_histories_cached_masks": {
+                           "value": e2e_engine_cached, "unit": "rows/s", "h2d_bytes_per_step": int(rows * (48 + 4)),
+                           "mask_cache": {"hits": hits, "misses": misses, "bytes_uploaded_in_all": up_bytes},
+                           "note": "masks through fns_b200_engine_pick_async_dl with grammar-state ids: every state was "
+                                   "seen in the warm-up, so a step uploads parameters and 4-byte slot numbers only"}},
     }
     if rank == 0:
         result["clocks"] = clock_info
     if rank == 0 and not args.skip_extras:
         result["batch1"] = batch1_latency(torch, dev, local)
+        result["config5_one_gpu"] = config5_one_gpu(torch, dev, local)
     if rank == 0 and world == 1 and not args.skip_extras:
         result["cpu_baseline"] = cpu_baseline(host[0], budget_s=args.cpu_seconds)
         result["reference_gpu_kernels"] = reference_gpu(torch, dev, host[0], dev_in[0])
@@ -341,7 +422,61 @@ def batch1_latency(torch, dev, local):
         res[name] = {"us_per_row_graph": graph_us, "us_per_row_stream": a.elapsed_time(b) * 1e3 / 200,
                      "bytes_per_row": w.row_bytes(), "plan": s.plan(0, w.vocab, 1, w.history.shape[1])}
         s.close()
+    # config 3: one verification window (3 draft positions + bonus = 4 rows), greedy, accept length on the device
+    sw = wl.spec_windows(seed=1, windows=1, n_draft=3)
+    s = Sampler(local, max_rows=4, max_vocab=sw.vocab, k_cap=64, max_history=0)
+    lg, dr = torch.from_numpy(sw.logits).to(dev), torch.from_numpy(sw.draft).to(dev)
+    pd = params_to_device(sw.params, dev)
+    toks, acc = torch.empty(4, dtype=torch.int32, device=dev), torch.empty(1, dtype=torch.int32, device=dev)
+    for _ in range(5):
+        s.verify_accept(lg, dr, pd, toks, acc)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(50):
+                s.verify_accept(lg, dr, pd, toks, acc)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(40):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    res["verify_window_4rows_greedy"] = {"us_per_window_graph": a.elapsed_time(b) * 1e3 / (40 * 50), "rows": 4,
+                                         "bytes_per_window": 4 * sw.vocab * 4 + 12 + 20,
+                                         "note": "select + draw kernel and the accept kernel per window"}
+    s.close()
     return res
+
+
+def config5_one_gpu(torch, dev, local):
+    """64 rows x V = 262,144 bf16, 50 % random mask, top-k 1024 / top-p / min-p on ONE GPU (no exchange)."""
+    from flintnsteel_b200 import workloads as wl
+    from flintnsteel_b200.sampler import Sampler, params_to_device
+
+    w = wl.large_vocab(seed=0, rows=64)
+    s = Sampler(local, max_rows=64, max_vocab=w.vocab, k_cap=1024, max_history=0)
+    lg = torch.from_numpy(w.logits.view(np.int16)).to(dev).view(torch.bfloat16)
+    m = torch.from_numpy(w.masks.view(np.int32)).to(dev)
+    pd = params_to_device(w.params, dev)
+    out = torch.empty(64, dtype=torch.int32, device=dev)
+    for _ in range(5):
+        s.sample_rows(lg, pd, out, masks=m)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(50):
+        s.sample_rows(lg, pd, out, masks=m)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / 50
+    s.close()
+    return {"us_per_call": us, "rows": 64, "vocab": w.vocab, "k": 1024, "bytes_per_call": 64 * w.row_bytes(),
+            "achieved_GBps": 64 * w.row_bytes() / us / 1e3}
 
 
 def host_threads() -> int:
@@ -462,7 +597,7 @@ def run_reference(args):
     from oracle.binding import Oracle
 
     o = Oracle()
-    sample_rows = 64
+    sample_rows = args.rows  # the same 256-row steps as the GPU arm
     w = wl.session_batch(seed=0, rows=sample_rows)
     threads, cores = 1, host_threads()
     for _ in range(max(args.warmup, 1)):
@@ -480,8 +615,8 @@ def run_reference(args):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_step": sample_rows, "vocab": w.vocab, "k_cap": 64,
                    "history_ids": int(w.history.shape[1]),
-                   "note": "each step is a 64-row sample of the 256-session batch; the reference's sampler is CUDA "
-                           "code, its CPU form is the restatement in oracle/fns_oracle.c"},
+                   "rows_per_gpu": sample_rows, "batches_rotated": 1, "parallelism": f"rows{world}",
+                   "note": "the reference's sampler is CUDA code; its CPU form is the restatement in oracle/fns_oracle.c"},
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
                          "sample": f"{K} steps of {sample_rows} rows, OpenMP over rows"},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -509,8 +644,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=256)
     ap.add_argument("--batches", type=int, default=4)
+    ap.add_argument("--repeats", type=int, default=30, help="timed regions of K steps each; the median is the value")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--skip-extras", action="store_true", help="only the headline numbers (for profiler runs)")
+    ap.add_argument("--skip-extras", action="store_true", help="no batch-1 / CPU / reference-kernel legs")
+    ap.add_argument("--only-headline", action="store_true", help="the timed regions only (for profiler runs)")
     ap.add_argument("--no-masks", action="store_true", help="every id allowed: the HBM-bound variant of the workload")
     ap.add_argument("--traffic", type=float, default=None,
                     help="dram bytes per select launch from an ncu capture (see profiles/), echoed into the line")
