@@ -34,7 +34,7 @@ METRIC = "sampler rows/s (V=151936 fp32, mask+penalties+top-k/p, 256 sessions pe
 WORKLOAD = "sessions256"
 # dram__bytes_read.sum + dram__bytes_write.sum per k_select launch, from the ncu captures summarised under profiles/
 NCU_TRAFFIC_BYTES = 25.3e6
-NCU_TRAFFIC_BYTES_DENSE = 194.1e6
+NCU_TRAFFIC_BYTES_DENSE = 162.8e6
 
 
 def measured_peaks():
