@@ -56,6 +56,8 @@ struct Slot {
     int32_t * draft_d;
     int32_t * accept_d;
     int32_t * mask_rows_d;
+    void * logits_d;      // staging for logits that arrive in host memory: one per slot, since the kernel of the older
+    size_t logits_bytes;  // pick may still read its copy; grows on first use (cudaFree waits for the device once)
     cudaEvent_t done;
     int rows;
     bool busy;
@@ -68,8 +70,6 @@ struct fns_b200_engine {
     fns_b200_sampler * sampler;
     Slot slot[kSlots];
     int head, tail;       // next slot to fill / oldest slot in flight
-    void * logits_d;      // staging for host logits, allocated on first use
-    size_t logits_bytes;
     int32_t * sess_history;      // [max_rows][max_history] device-side session histories
     int32_t * sess_history_len;  // [max_rows]
     int32_t * counts_d;
@@ -112,7 +112,7 @@ void free_slot(Slot & s) {
     cudaFreeHost(s.masks_h); cudaFreeHost(s.history_h); cudaFreeHost(s.history_len_h); cudaFreeHost(s.params_h);
     cudaFreeHost(s.tokens_h); cudaFreeHost(s.draft_h); cudaFreeHost(s.accept_h); cudaFreeHost(s.mask_rows_h);
     cudaFree(s.masks_d); cudaFree(s.history_d); cudaFree(s.history_len_d); cudaFree(s.params_d);
-    cudaFree(s.tokens_d); cudaFree(s.draft_d); cudaFree(s.accept_d); cudaFree(s.mask_rows_d);
+    cudaFree(s.tokens_d); cudaFree(s.draft_d); cudaFree(s.accept_d); cudaFree(s.mask_rows_d); cudaFree(s.logits_d);
     if (s.done) cudaEventDestroy(s.done);
 }
 
@@ -203,7 +203,6 @@ int fns_b200_engine_destroy(fns_b200_engine * e) {
     Dev g(e->device);
     cudaDeviceSynchronize();
     for (int i = 0; i < kSlots; ++i) free_slot(e->slot[i]);
-    cudaFree(e->logits_d);
     cudaFree(e->sess_history);
     cudaFree(e->sess_history_len);
     cudaFree(e->counts_d);
@@ -242,16 +241,16 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
         lg = in_place;  // the kernel loads the allowed vectors over PCIe; nothing else of the logits moves
     } else if (logits_on_host & FNS_B200_HOST_LOGITS) {
         const size_t bytes = ((size_t) (rows - 1) * row_stride + e->vocab) * esz;
-        if (bytes > e->logits_bytes) {
-            cudaFree(e->logits_d);
-            e->logits_d = nullptr;
-            e->logits_bytes = 0;
-            if ((err = cudaMalloc(&e->logits_d, bytes)) != cudaSuccess) return ecuda(e, err, "logits staging");
-            e->logits_bytes = bytes;
+        if (bytes > s.logits_bytes) {
+            cudaFree(s.logits_d);
+            s.logits_d = nullptr;
+            s.logits_bytes = 0;
+            if ((err = cudaMalloc(&s.logits_d, bytes)) != cudaSuccess) return ecuda(e, err, "logits staging");
+            s.logits_bytes = bytes;
         }
-        if ((err = cudaMemcpyAsync(e->logits_d, logits, bytes, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        if ((err = cudaMemcpyAsync(s.logits_d, logits, bytes, cudaMemcpyHostToDevice, st)) != cudaSuccess)
             return ecuda(e, err, "logits copy");
-        lg = e->logits_d;
+        lg = s.logits_d;
     }
     if (masks_host && (err = bring(s.masks_h, s.masks_d, masks_host, (size_t) rows * e->words, stable, st)) != cudaSuccess)
         return ecuda(e, err, "mask copy");

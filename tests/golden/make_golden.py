@@ -235,4 +235,6 @@ def main(out_dir: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <output directory>   (on a machine with a B200)")
+    main(sys.argv[1])
