@@ -37,7 +37,7 @@ struct ClusterShared {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a) {
+__global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs a) {
     namespace cg = cooperative_groups;
     constexpr int NT = kClusterThreads, kWarps = NT / 32;
     constexpr int VEC = 16 / (int) sizeof(T);
@@ -89,39 +89,52 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
         tkey[i] = kNoKey;
         tcnt[i] = 0u;
     }
+    // 1. the slice's bit set.  Without a mask it depends on nothing in global memory and is made here, ahead of the wait.
+    const uint32_t tail_bits = (n_s & 31) ? (1u << (n_s & 31)) - 1u : 0xffffffffu;
+    if (!a.masks)
+        for (int w = tid; w < a.slice_len / 32; w += NT) eff[w] = w < words ? (w == words - 1 ? tail_bits : 0xffffffffu) : 0u;
+    __syncthreads();
     // Launched with programmatic stream serialisation: nothing is read from global memory before the previous
     // kernel of the stream has finished; what precedes this line overlaps its tail.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // (the row's parameters and the first mask words first: their latency passes while the copies are being issued)
+    fns_b200_params p = a.params ? a.params[win] : a.p0;
+    int n_hist = (a.history && a.history_len) ? a.history_len[win] : 0;
+    const uint32_t * mrow = a.masks ? a.masks + (size_t) (a.mask_rows ? a.mask_rows[row] : row) * a.mask_stride + (lo >> 5) : nullptr;
+    constexpr int kMaskRegs = 4;  // mask words a thread fetches ahead (slices of up to 32,768 elements: all of them)
+    uint32_t mreg[kMaskRegs];
+    if (mrow) {
+#pragma unroll
+        for (int q = 0; q < kMaskRegs; ++q) mreg[q] = tid + q * NT < words ? mrow[tid + q * NT] : 0u;
+    }
     const T * x = reinterpret_cast<const T *>(a.logits) + (size_t) row * a.row_stride + lo;
     const uint32_t id0 = (uint32_t) (a.id_base + lo);
-    // the slice: whole 16-byte vectors by one bulk copy, a ragged end by plain loads
+    const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
+    const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
+    // The slice: whole 16-byte vectors by one bulk copy, a ragged end by plain loads.  The row's history ids come into
+    // shared memory with one more bulk copy (when the list is 16-byte aligned): every later walk over them - the
+    // scatter, the occurrence count - reads shared memory.  The two copies are issued by threads of different warps.
     const uint32_t bulk_bytes = ((uint32_t) n_s * (uint32_t) sizeof(T)) & ~15u;
+    const bool hist_staged = hrow && a.own_cap > 0 && a.hist_cap > 0 && (reinterpret_cast<uintptr_t>(hrow) & 15u) == 0;
     if (tid == 0) {
         if (bulk_bytes) bulk_load(data, x, bulk_bytes, &cs.bar);
         mbar_arrive_expect(&cs.bar, bulk_bytes);
-    }
-    for (int e = (int) (bulk_bytes / sizeof(T)) + tid; e < n_s; e += NT) data[e] = x[e];
-    const uint32_t * mrow = a.masks ? a.masks + (size_t) (a.mask_rows ? a.mask_rows[row] : row) * a.mask_stride + (lo >> 5) : nullptr;
-    const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
-    const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
-    fns_b200_params p = a.params ? a.params[win] : a.p0;
-    int n_hist = (a.history && a.history_len) ? a.history_len[win] : 0;
-    // the row's history ids come into shared memory with one more bulk copy (when the list is 16-byte aligned):
-    // every later walk over them - the scatter, the occurrence count - reads shared memory
-    const bool hist_staged = hrow && a.own_cap > 0 && a.hist_cap > 0 && (reinterpret_cast<uintptr_t>(hrow) & 15u) == 0;
-    if (tid == 0) {
+    } else if (tid == 32) {
         const uint32_t hb = hist_staged ? (uint32_t) a.hist_cap * 4u : 0u;  // (hist_cap: the stride rounded down to 4 ids)
         if (hb) bulk_load(hid, hrow, hb, &cs.hbar);
         mbar_arrive_expect(&cs.hbar, hb);
     }
-
-    // 1. the slice's bit set
-    {
-        const uint32_t tail = (n_s & 31) ? (1u << (n_s & 31)) - 1u : 0xffffffffu;
-        for (int w = tid; w < a.slice_len / 32; w += NT) {
-            uint32_t m = w < words ? (mrow ? mrow[w] : 0xffffffffu) : 0u;
-            if (w == words - 1) m &= tail;
+    for (int e = (int) (bulk_bytes / sizeof(T)) + tid; e < n_s; e += NT) data[e] = x[e];
+    if (mrow) {
+#pragma unroll
+        for (int q = 0; q < kMaskRegs; ++q) {
+            const int w = tid + q * NT;
+            if (w < a.slice_len / 32) eff[w] = w == words - 1 ? mreg[q] & tail_bits : mreg[q];
+        }
+        for (int w = tid + kMaskRegs * NT; w < a.slice_len / 32; w += NT) {
+            uint32_t m = w < words ? mrow[w] : 0u;
+            if (w == words - 1) m &= tail_bits;
             eff[w] = m;
         }
     }
@@ -130,7 +143,7 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
     const bool use_hist = any_pen && a.own_cap > 0 && n_s > 0;
     n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
     const int n_pen = n_hist + (a.draft ? col : 0);
-    __syncthreads();
+    if (mrow) __syncthreads();
 
     // 2. history ids of the slice clear their bits; the thread that clears a bit owns the id
     auto pen_id = [&](int j) -> int32_t {  // id j of the row's history followed by the window's draft prefix
@@ -139,27 +152,41 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
     };
     if (use_hist && n_pen > 0) {
         if (hist_staged && !mbar_wait(&cs.hbar, 0u) && a.err) atomicExch(a.err, 3);
-        // sixteen ids per thread at a time: first every id is tested and its bit cleared (nothing in these tests
-        // depends on another, so they overlap), then the warp reserves list places for all its owners at once
-        constexpr int HB = 16;
-#pragma unroll 1
-        for (int j0 = 0; j0 < n_pen; j0 += HB * NT) {
-            uint32_t won = 0u;  // bit u: this thread owns id j0 + u * NT + tid
+        // Sixteen ids per thread at a time, as four vectors of four from shared memory.  The steps are kept apart - all
+        // loads, all range tests, all reads of the bit set, then the atomics - because an atomic in between would keep
+        // the compiler from moving the later loads ahead of it, and the ids would be handled one after the other.
+        const bool vec_ok = hist_staged && n_hist <= a.hist_cap;  // every history id is in shared memory
+        auto claim = [&](auto hb, int j0) {
+            constexpr int HB = decltype(hb)::value;
+            int32_t id[HB];
 #pragma unroll
-            for (int u = 0; u < HB; ++u) {
-                const int j = j0 + u * NT + tid;
-                if (j0 + u * NT >= n_pen) break;  // uniform
-                const int32_t id = pen_id(j);
-                const uint32_t off = (uint32_t) (id - a.id_base - lo);
-                if (off < (uint32_t) n_s && id >= a.id_base) {
-                    const uint32_t bit = 1u << (off & 31);
-                    // (a plain read first: ids that the mask excludes, and repeats, cost no atomic; a stale 1 is settled by
-                    // the atomic itself, and a 0 stays 0)
-                    if ((eff[off >> 5] & bit) && (atomicAnd(&eff[off >> 5], ~bit) & bit)) won |= 1u << u;
+            for (int q = 0; q < HB / 4; ++q) {
+                const int jb = j0 + q * 4 * NT + tid * 4;
+                if (vec_ok && jb + 4 <= n_hist) {
+                    const int4 v = *reinterpret_cast<const int4 *>(hid + jb);
+                    id[4 * q] = v.x; id[4 * q + 1] = v.y; id[4 * q + 2] = v.z; id[4 * q + 3] = v.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) id[4 * q + e] = jb + e < n_pen ? pen_id(jb + e) : -1;
                 }
             }
+            uint32_t offv[HB], wv[HB], inr = 0u, won = 0u;  // bit u of won: this thread owns id[u]
+#pragma unroll
+            for (int u = 0; u < HB; ++u) {
+                offv[u] = (uint32_t) (id[u] - a.id_base - lo);
+                if (offv[u] < (uint32_t) n_s && id[u] >= a.id_base) inr |= 1u << u;
+            }
+#pragma unroll
+            for (int u = 0; u < HB; ++u) wv[u] = ((inr >> u) & 1u) ? eff[offv[u] >> 5] : 0u;
+#pragma unroll
+            for (int u = 0; u < HB; ++u) {
+                const uint32_t bit = 1u << (offv[u] & 31);
+                // (the plain read came first: ids that the mask excludes, and repeats, cost no atomic; a stale 1 is settled
+                // by the atomic itself, and a 0 stays 0)
+                if ((wv[u] & bit) && (atomicAnd(&eff[offv[u] >> 5], ~bit) & bit)) won |= 1u << u;
+            }
             const uint32_t mine_n = (uint32_t) __popc(won);
-            if (__ballot_sync(kFull, mine_n != 0u) == 0u) continue;
+            if (__ballot_sync(kFull, mine_n != 0u) == 0u) return;
             uint32_t upto = mine_n;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -169,8 +196,14 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
             uint32_t at = 0u;
             if (lane == 31) at = atomicAdd(&sh.n_own, upto);
             at = __shfl_sync(kFull, at, 31) + upto - mine_n;
-            for (uint32_t q = won; q; q &= q - 1u) own[at++] = (uint32_t) (pen_id(j0 + (__ffs(q) - 1) * NT + tid) - a.id_base - lo);
-        }
+#pragma unroll
+            for (int u = 0; u < HB; ++u)
+                if ((won >> u) & 1u) own[at++] = offv[u];
+        };
+        int j0 = 0;
+#pragma unroll 1
+        for (; n_pen - j0 > 4 * NT; j0 += 16 * NT) claim(std::integral_constant<int, 16>{}, j0);
+        if (j0 < n_pen) claim(std::integral_constant<int, 4>{}, j0);  // (a short list, or a short rest: one vector per thread)
     }
     __syncthreads();
     const int n_own = use_hist ? (int) sh.n_own : 0;
@@ -197,15 +230,26 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
             }
         }
     };
-    float tmax = -INFINITY;
+    // (every thread also keeps which of its vectors holds its maximum, and the largest value of its other vectors: the
+    // candidate pass then re-reads one vector per thread, the others only if they can matter)
+    float tmax = -INFINITY, tmax2 = -INFINITY;
+    int vmax_at = tid;
 #pragma unroll 4
     for (int v = tid; v < n_vec; v += NT) {
         const uint32_t bits = vec_bits(v);
         float xv[VEC];
         vec_load(v, xv);
+        float vm = -INFINITY;
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
-            if (((bits >> j) & 1u) && fabsf(xv[j]) <= FLT_MAX) tmax = fmaxf(tmax, xv[j]);  // finite and allowed (src/kernels.cu:629-639)
+            if (((bits >> j) & 1u) && fabsf(xv[j]) <= FLT_MAX) vm = fmaxf(vm, xv[j]);  // finite and allowed (src/kernels.cu:629-639)
+        if (vm > tmax) {
+            tmax2 = tmax;
+            tmax = vm;
+            vmax_at = v;
+        } else {
+            tmax2 = fmaxf(tmax2, vm);
+        }
     }
     // the two largest thread maxima of every warp go to CTA 0: 2 * 8 * 16 witnesses, all different elements
     {
@@ -214,7 +258,8 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
         const uint32_t holders = __ballot_sync(kFull, w == w1);
         if (lane == __ffs(holders) - 1) w = 0u;
         const uint32_t w2 = __reduce_max_sync(kFull, w);
-        if (lane < 2) cs0->wit[(rank * kWarps + warp) * 2 + lane] = lane == 0 ? w1 : w2;
+        // every CTA receives the witnesses (lane l stores into CTA l / 2): the bound search then reads its own memory
+        cluster.map_shared_rank(&cs, lane >> 1)->wit[(rank * kWarps + warp) * 2 + (lane & 1)] = (lane & 1) ? w2 : w1;
     }
     cluster.sync();
 
@@ -224,7 +269,7 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
     if (warp == 0) {
         uint32_t w8[8];
         {
-            const uint4 lo4 = *reinterpret_cast<const uint4 *>(&cs0->wit[lane * 8]), hi4 = *reinterpret_cast<const uint4 *>(&cs0->wit[lane * 8 + 4]);
+            const uint4 lo4 = *reinterpret_cast<const uint4 *>(&cs.wit[lane * 8]), hi4 = *reinterpret_cast<const uint4 *>(&cs.wit[lane * 8 + 4]);
             w8[0] = lo4.x; w8[1] = lo4.y; w8[2] = lo4.z; w8[3] = lo4.w;
             w8[4] = hi4.x; w8[5] = hi4.y; w8[6] = hi4.z; w8[7] = hi4.w;
         }
@@ -249,12 +294,23 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
                 const int top = 31 - __clz((int) varying);
                 const int stop = top > 13 ? top - 13 : 0;
 #pragma unroll 1
-                for (int bit = top; bit >= stop; --bit) {
-                    const uint32_t cand = bw | (1u << bit);
-                    uint32_t c = 0u;
+                for (int bit = top; bit >= stop; bit -= 2) {  // two bits per step: three counts that do not wait for one another
+                    const uint32_t b1 = 1u << bit, b0 = bit > stop ? 1u << (bit - 1) : 0u;
+                    uint32_t c1 = 0u, c10 = 0u, c0 = 0u;
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) c += w8[q] >= cand ? 1u : 0u;
-                    if (__reduce_add_sync(kFull, c) >= (uint32_t) k) bw = cand;
+                    for (int q = 0; q < 8; ++q) {
+                        c1 += w8[q] >= (bw | b1) ? 1u : 0u;
+                        c10 += w8[q] >= (bw | b1 | b0) ? 1u : 0u;
+                        c0 += w8[q] >= (bw | b0) ? 1u : 0u;
+                    }
+                    c1 = __reduce_add_sync(kFull, c1);
+                    c10 = __reduce_add_sync(kFull, c10);
+                    c0 = __reduce_add_sync(kFull, c0);
+                    uint32_t tot = 0xffffffffu;
+                    if (c10 >= (uint32_t) k) bw |= b1 | b0, tot = c10;
+                    else if (c1 >= (uint32_t) k) bw |= b1, tot = c1;
+                    else if (c0 >= (uint32_t) k) bw |= b0, tot = c0;
+                    if (tot <= (uint32_t) k + 4u) break;  // close enough: at most four witnesses too many
                 }
             }
         }
@@ -296,13 +352,25 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
                 uint32_t fo[8];
 #pragma unroll
                 for (int q = 0; q < 8; ++q) fo[q] = (uint32_t) q < n_few ? few[1 + q] : 0xffffffffu;
-#pragma unroll 4
-                for (int t = tid; t < n_pen; t += NT) {
-                    const int32_t id = pen_id(t);
-                    const uint32_t o = id >= a.id_base ? (uint32_t) (id - a.id_base - lo) : 0xfffffffeu;
+                const bool vec_ok = hist_staged && n_hist <= a.hist_cap;
+#pragma unroll 2
+                for (int t0 = tid * 4; t0 < n_pen; t0 += 4 * NT) {  // four ids per thread and round; matches first, atomics after
+                    int32_t id4[4];
+                    if (vec_ok && t0 + 4 <= n_hist) {
+                        const int4 v = *reinterpret_cast<const int4 *>(hid + t0);
+                        id4[0] = v.x; id4[1] = v.y; id4[2] = v.z; id4[3] = v.w;
+                    } else {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (o == fo[q]) atomicAdd(&few[9 + q], 1u);
+                        for (int e = 0; e < 4; ++e) id4[e] = t0 + e < n_pen ? pen_id(t0 + e) : -1;
+                    }
+                    uint32_t hits = 0u;  // bit 8 e + q: id e is the list's entry q
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t o = id4[e] >= a.id_base ? (uint32_t) (id4[e] - a.id_base - lo) : 0xfffffffeu;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) hits |= o == fo[q] ? 1u << (8 * e + q) : 0u;
+                    }
+                    for (; hits; hits &= hits - 1u) atomicAdd(&few[9 + ((__ffs(hits) - 1) & 7)], 1u);
                 }
                 __syncthreads();
                 if (live) v = penalised(raw, (float) few[9 + place]);
@@ -354,22 +422,48 @@ __global__ void __launch_bounds__(kClusterThreads) k_cluster(const SelectArgs a)
     };
     {
         for (int j0 = 0; j0 < n_own; j0 += NT) offer_local(history_key(j0 + tid));
-        // Few threads hold a maximum that reaches the bound.  For each of them, the lanes of its warp take one of its
-        // vectors each (thread t owns vectors t, t + NT, t + 2 NT, ...), so a holder costs one round, not one per vector.
-        for (uint32_t holders = __ballot_sync(kFull, tmax >= thr_v); holders; holders &= holders - 1u) {
-            const int src = __ffs(holders) - 1;
-            for (int q0 = 0; warp * 32 + src + q0 * NT < n_vec; q0 += 32) {
-                const int v = warp * 32 + src + (q0 + lane) * NT;
-                const uint32_t bits = v < n_vec ? vec_bits(v) : 0u;
-                float xv[VEC];
-                uint32_t hit = 0u;
-                if (bits) {
-                    vec_load(v, xv);
+        // The elements that reach the bound: one reservation per round of the warp, whatever the number of hits.
+        auto offer_vec = [&](uint32_t hit, const float (&xv)[VEC], int v) {  // every lane calls it; hit: elements of vector v to offer
+            uint32_t total = 0u, pos[VEC];
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) hit |= (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) ? 1u << j : 0u;
+            for (int j = 0; j < VEC; ++j) {
+                const uint32_t b = __ballot_sync(kFull, (hit >> j) & 1u);
+                pos[j] = total + (uint32_t) __popc(b & ((1u << lane) - 1u));
+                total += (uint32_t) __popc(b);
+            }
+            if (total == 0u) return;
+            uint32_t base = 0u;
+            if (lane == 0) base = atomicAdd(&sh.n_cand, total);
+            base = __shfl_sync(kFull, base, 0);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                if (((hit >> j) & 1u) && base + pos[j] < (uint32_t) kClusterLocal) lbuf[base + pos[j]] = make_key(xv[j], id0 + (uint32_t) (v * VEC + j));
+        };
+        auto hits_of = [&](int v, float (&xv)[VEC]) -> uint32_t {
+            const uint32_t bits = v < n_vec ? vec_bits(v) : 0u;
+            uint32_t hit = 0u;
+            if (bits) {
+                vec_load(v, xv);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) hit |= (((bits >> j) & 1u) && xv[j] >= thr_v && xv[j] <= FLT_MAX) ? 1u << j : 0u;
+            }
+            return hit;
+        };
+        // A thread whose maximum reaches the bound offers the hits of that vector: one round for the whole warp.  Only a
+        // thread with a second vector that reaches the bound has all its vectors looked at.
+        const bool holder = tmax >= thr_v;
+        if (__any_sync(kFull, holder)) {
+            float xv[VEC];
+            offer_vec(holder ? hits_of(vmax_at, xv) : 0u, xv, vmax_at);
+            // (its other vectors are taken by the lanes of the warp, one each: thread t owns vectors t, t + NT, ...)
+            for (uint32_t rest = __ballot_sync(kFull, holder && tmax2 >= thr_v); rest; rest &= rest - 1u) {
+                const int src = __ffs(rest) - 1;
+                const int done = __shfl_sync(kFull, vmax_at, src);
+#pragma unroll 1
+                for (int q0 = 0; warp * 32 + src + q0 * NT < n_vec; q0 += 32) {
+                    const int v = warp * 32 + src + (q0 + lane) * NT;
+                    offer_vec(v != done ? hits_of(v, xv) : 0u, xv, v);
                 }
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) offer_local(((hit >> j) & 1u) ? make_key(xv[j], id0 + (uint32_t) (v * VEC + j)) : 0ull);
             }
         }
         __syncthreads();

@@ -202,6 +202,71 @@ __device__ uint64_t * merge_runs_pow2(uint64_t * a, uint64_t * b, int runs, int 
     return a;
 }
 
+// Sorts up to NT * KPT keys into descending order with the keys in registers: a bitonic network in which thread t holds
+// elements t * KPT .. t * KPT + KPT - 1.  Exchanges at a distance below KPT stay inside the thread, those below
+// 32 * KPT go through warp shuffles, and only the few steps that pair elements of different warps go through shared
+// memory (one barrier each; two buffers of NT * KPT keys take turns, so a buffer is not written while a slower warp
+// still reads it).  in[0 .. n) are the keys (0 = empty, sorts last); the first `take` keys of the result go to out.
+// in may be x0 (it is read before anything is written).  All NT threads; block synchronised on entry.
+template <int NT, int KPT>
+__device__ void block_sort_regs(const uint64_t * in, int n, uint64_t * x0, uint64_t * x1, uint64_t * out, int take) {
+    static_assert(KPT == 2 || KPT == 4, "two or four keys per thread");
+    constexpr int M = NT * KPT;
+    const int tid = threadIdx.x;
+    uint64_t q[KPT];
+#pragma unroll
+    for (int j = 0; j < KPT; ++j) q[j] = tid * KPT + j < n ? in[tid * KPT + j] : 0ull;
+    __syncthreads();  // (in may be an exchange buffer)
+    auto inside = [&](int i, int j, bool desc) {
+        if ((q[i] < q[j]) == desc) {
+            const uint64_t t = q[i];
+            q[i] = q[j];
+            q[j] = t;
+        }
+    };
+    uint64_t * xb = x0;
+#pragma unroll 1
+    for (int size = 2; size <= M; size <<= 1) {
+#pragma unroll 1
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const bool desc = ((tid * KPT) & size) == 0;  // (the same for all keys of a thread once size >= KPT; below, see inside)
+            if (stride < KPT) {
+                if (KPT == 2) {
+                    inside(0, 1, desc);
+                } else if (stride == 1) {
+                    inside(0, 1, size == 2 ? true : desc);
+                    inside(2, 3, size == 2 ? false : desc);
+                } else {
+                    inside(0, 2, desc);
+                    inside(1, 3, desc);
+                }
+            } else if (stride < 32 * KPT) {
+                const int lx = stride / KPT;
+                const bool keep_max = (((tid * KPT) & stride) == 0) == desc;
+#pragma unroll
+                for (int j = 0; j < KPT; ++j) {
+                    const uint64_t other = __shfl_xor_sync(kFull, q[j], lx);
+                    q[j] = keep_max ? (other > q[j] ? other : q[j]) : (other < q[j] ? other : q[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < KPT; ++j) xb[tid * KPT + j] = q[j];
+                __syncthreads();
+                const bool keep_max = (((tid * KPT) & stride) == 0) == desc;
+#pragma unroll
+                for (int j = 0; j < KPT; ++j) {
+                    const uint64_t other = xb[(tid * KPT + j) ^ stride];
+                    q[j] = keep_max ? (other > q[j] ? other : q[j]) : (other < q[j] ? other : q[j]);
+                }
+                xb = xb == x0 ? x1 : x0;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < KPT; ++j)
+        if (tid * KPT + j < take) out[tid * KPT + j] = q[j];
+}
+
 // Sorts a[0 .. m) (m a power of two, in shared memory) into descending order: a bitonic network, one barrier per
 // step.  All NT threads; block synchronised on entry and exit.
 template <int NT>
@@ -298,6 +363,84 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         sh.n_vl = 0u;
         sh.n_seg = 0u;
     }
+    // 1. The bit set (bit e: element e is allowed and inside the row), the chunk map and the list of stages that have
+    // an allowed id.  A chunk is 16 words = 4 neighbouring lanes, so a warp covers 8 chunks of one stage and writes
+    // their bits as one byte: no atomics.  (Doing this ahead of the dependency wait for rows without a mask was
+    // measured: it slows the previous kernel's tail on the same SM by more than it saves.)
+    auto build_bits = [&](const uint32_t * mrow) {
+        {
+            const int words = (V + 31) >> 5;
+            const int eff_words = n_stages * kStageWords;
+            const uint32_t tail = (V & 31) ? (1u << (V & 31)) - 1u : 0xffffffffu;
+            const bool wide = mrow && (reinterpret_cast<uintptr_t>(mrow) & 15u) == 0;
+            constexpr int IT = 4;  // rounds whose loads are all issued before the first is used (rows up to 262,144)
+            auto fetch = [&](int w0, uint32_t (&m)[4]) {
+                if (!mrow) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) m[q] = w0 + q < words ? 0xffffffffu : 0u;
+                } else if (wide && w0 + 4 <= words) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(mrow + w0);
+                    m[0] = v.x;
+                    m[1] = v.y;
+                    m[2] = v.z;
+                    m[3] = v.w;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) m[q] = w0 + q < words ? mrow[w0 + q] : 0u;
+                }
+            };
+            auto settle = [&](int w0, uint32_t (&m)[4]) {  // (every lane of the warp is here: eff_words is a multiple of 128)
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (w0 + q == words - 1) m[q] &= tail;
+                *reinterpret_cast<uint4 *>(eff + w0) = make_uint4(m[0], m[1], m[2], m[3]);
+                const uint32_t b = __ballot_sync(kFull, (m[0] | m[1] | m[2] | m[3]) != 0u);
+                if (lane == 0) {
+                    uint32_t c8 = 0u;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) c8 |= ((b >> (4 * c)) & 15u) ? (1u << c) : 0u;
+                    reinterpret_cast<uint8_t *>(chunk_bits)[w0 >> 7] = (uint8_t) c8;  // byte = 128 words = half a stage
+                }
+            };
+            uint32_t mw[IT][4];
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int w0 = (it * NT + tid) * 4;
+                if (w0 < eff_words) fetch(w0, mw[it]);
+            }
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int w0 = (it * NT + tid) * 4;
+                if (w0 < eff_words) settle(w0, mw[it]);
+            }
+            for (int w0 = (IT * NT + tid) * 4; w0 < eff_words; w0 += NT * 4) {
+                uint32_t m[4];
+                fetch(w0, m);
+                settle(w0, m);
+            }
+        }
+        {
+            uint4 * z = reinterpret_cast<uint4 *>(cmax);
+            for (int i = tid; i < n_stages * NT / 8; i += NT) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto list_stages = [&](const uint32_t * mrow) {  // warp 0; with a mask the first copies start here
+        if (warp == 0) {
+            const uint32_t below = (1u << lane) - 1u;
+            int base = 0;
+            for (int s0 = 0; s0 < n_stages; s0 += 32) {
+                const int s = s0 + lane;
+                const bool live = s < n_stages && chunk_bits[s] != 0u;
+                const uint32_t b = __ballot_sync(kFull, live);
+                if (live) stage_list[base + __popc(b & below)] = (uint16_t) s;
+                base += __popc(b);
+            }
+            if (lane == 0) sh.n_seg = (uint32_t) base;
+            __syncwarp();
+            if (lane == 0 && mrow)
+                for (int u = 0; u < depth && u < base; ++u) issue_stage(stage_list[u], u, chunk_bits[stage_list[u]]);
+        }
+    };
     // Launched with programmatic stream serialisation: this block may start while the previous kernel of the stream
     // still drains, and the next kernel's blocks may take the places of blocks that have exited (they wait here
     // too).  Nothing is read from global memory before the previous kernel has finished.
@@ -307,7 +450,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     // without a mask every chunk is wanted: the first stages start now
     if (tid == 0 && !mrow)
         for (int u = 0; u < depth && u < n_stages; ++u) issue_stage(u, u, 0xffffu);
-
     // Everything whose address is known is requested before anything is waited for.
     const int32_t * hrow = a.history ? a.history + (size_t) win * a.history_stride : nullptr;
     const int32_t * drow = a.draft ? a.draft + (size_t) win * a.n_draft : nullptr;
@@ -321,86 +463,14 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
             if (j < (int) a.history_stride) ids0[u] = hrow[j];
         }
     }
-
-    // 1. The bit set (bit e: element e is allowed and inside the row) and the chunk map.  A chunk is 16 words = 4
-    // neighbouring lanes, so a warp covers 8 chunks of one stage and writes their bits as one byte: no atomics.
-    {
-        const int words = (V + 31) >> 5;
-        const int eff_words = n_stages * kStageWords;
-        const uint32_t tail = (V & 31) ? (1u << (V & 31)) - 1u : 0xffffffffu;
-        const bool wide = mrow && (reinterpret_cast<uintptr_t>(mrow) & 15u) == 0;
-        constexpr int IT = 4;  // rounds whose loads are all issued before the first is used (rows up to 262,144)
-        auto fetch = [&](int w0, uint32_t (&m)[4]) {
-            if (!mrow) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) m[q] = w0 + q < words ? 0xffffffffu : 0u;
-            } else if (wide && w0 + 4 <= words) {
-                const uint4 v = *reinterpret_cast<const uint4 *>(mrow + w0);
-                m[0] = v.x;
-                m[1] = v.y;
-                m[2] = v.z;
-                m[3] = v.w;
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) m[q] = w0 + q < words ? mrow[w0 + q] : 0u;
-            }
-        };
-        auto settle = [&](int w0, uint32_t (&m)[4]) {  // (every lane of the warp is here: eff_words is a multiple of 128)
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                if (w0 + q == words - 1) m[q] &= tail;
-            *reinterpret_cast<uint4 *>(eff + w0) = make_uint4(m[0], m[1], m[2], m[3]);
-            const uint32_t b = __ballot_sync(kFull, (m[0] | m[1] | m[2] | m[3]) != 0u);
-            if (lane == 0) {
-                uint32_t c8 = 0u;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) c8 |= ((b >> (4 * c)) & 15u) ? (1u << c) : 0u;
-                reinterpret_cast<uint8_t *>(chunk_bits)[w0 >> 7] = (uint8_t) c8;  // byte = 128 words = half a stage
-            }
-        };
-        uint32_t mw[IT][4];
-#pragma unroll
-        for (int it = 0; it < IT; ++it) {
-            const int w0 = (it * NT + tid) * 4;
-            if (w0 < eff_words) fetch(w0, mw[it]);
-        }
-#pragma unroll
-        for (int it = 0; it < IT; ++it) {
-            const int w0 = (it * NT + tid) * 4;
-            if (w0 < eff_words) settle(w0, mw[it]);
-        }
-        for (int w0 = (IT * NT + tid) * 4; w0 < eff_words; w0 += NT * 4) {
-            uint32_t m[4];
-            fetch(w0, m);
-            settle(w0, m);
-        }
-    }
-    {
-        uint4 * z = reinterpret_cast<uint4 *>(cmax);
-        for (int i = tid; i < n_stages * NT / 8; i += NT) z[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
+    build_bits(mrow);
     const int k = p.temperature <= 0.0f ? 1 : clamp_k(p.top_k, a.k_cap);
     const bool any_pen = p.repetition != 1.0f || p.presence != 0.0f || p.frequency != 0.0f;
     const bool use_hist = any_pen && a.own_cap > 0;
     n_hist = n_hist < 0 ? 0 : (n_hist > (int) a.history_stride ? (int) a.history_stride : n_hist);
     const int n_pen = n_hist + (a.draft ? col : 0);
     __syncthreads();
-    // the stages that have an allowed id, in order; with a mask the first copies start here
-    if (warp == 0) {
-        const uint32_t below = (1u << lane) - 1u;
-        int base = 0;
-        for (int s0 = 0; s0 < n_stages; s0 += 32) {
-            const int s = s0 + lane;
-            const bool live = s < n_stages && chunk_bits[s] != 0u;
-            const uint32_t b = __ballot_sync(kFull, live);
-            if (live) stage_list[base + __popc(b & below)] = (uint16_t) s;
-            base += __popc(b);
-        }
-        if (lane == 0) sh.n_seg = (uint32_t) base;
-        __syncwarp();
-        if (lane == 0 && mrow)
-            for (int u = 0; u < depth && u < base; ++u) issue_stage(stage_list[u], u, chunk_bits[stage_list[u]]);
-    }
+    list_stages(mrow);
 
     // 2. Penalties: every history id (plus the draft prefix of a verification column) clears its bit, so the
     // streaming pass never counts it; the thread that finds the bit still set owns the id and lists it once.
@@ -414,17 +484,23 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                 if (j0 == 0 && hrow) ids[u] = j < n_hist ? ids0[u] : (j < n_pen ? drow[j - n_hist] : -1);
                 else ids[u] = j < n_hist ? hrow[j] : (j < n_pen ? drow[j - n_hist] : -1);
             }
-            uint32_t offs[4], pre[4], total = 0u;
+            // (the steps are kept apart - plain reads of the bit set, then the atomics, then the votes - because an atomic
+            // in between would keep the compiler from moving the later reads ahead of it)
+            uint32_t offs[4], seen[4], pre[4], total = 0u;
             bool mine[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 offs[u] = (uint32_t) (ids[u] - a.id_base);
-                mine[u] = false;
-                if (offs[u] < (uint32_t) V && ids[u] >= a.id_base) {
-                    const uint32_t bit = 1u << (offs[u] & 31);
-                    // (a plain read first: a stale 1 is settled by the atomic itself, and a 0 stays 0)
-                    if (eff[offs[u] >> 5] & bit) mine[u] = (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
-                }
+                seen[u] = (offs[u] < (uint32_t) V && ids[u] >= a.id_base) ? eff[offs[u] >> 5] : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t bit = 1u << (offs[u] & 31);
+                // (a plain read came first: a stale 1 is settled by the atomic itself, and a 0 stays 0)
+                mine[u] = (seen[u] & bit) && (atomicAnd(&eff[offs[u] >> 5], ~bit) & bit) != 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
                 const uint32_t b = __ballot_sync(kFull, mine[u]);
                 pre[u] = total + (uint32_t) __popc(b & below);
                 total += (uint32_t) __popc(b);
@@ -914,6 +990,13 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     while (4 * pow2_runs < n) pow2_runs <<= 1;
     if (n <= kRankSelectMax) {
         got = block_rank_select<NT>(buf, n, k, sorted);
+    } else if (n <= 2 * NT && a.cap >= 4 * NT) {
+        // a longer list (k beyond 384): sorted as it is, in registers
+        got = n < k ? n : k;
+        block_sort_regs<NT, 2>(buf, n, buf, buf + 2 * NT, sorted, got);
+    } else if (n <= 4 * NT && a.cap >= 8 * NT) {
+        got = n < k ? n : k;
+        block_sort_regs<NT, 4>(buf, n, buf, buf + 4 * NT, sorted, got);
     } else if (8 * pow2_runs <= a.cap) {
         // a long list (k beyond 384): sorted as it is, by merging.  Every thread orders four keys in registers, the
         // runs of four (a power of two of them: empty runs fill up) are merged pairwise in the two halves of the

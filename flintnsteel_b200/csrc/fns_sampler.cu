@@ -35,6 +35,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <type_traits>
 #include <mutex>
 #include <vector>
 
@@ -311,6 +312,79 @@ __device__ int merge_ranked(const uint64_t * buf, int lists, int len, uint64_t *
     return total < k ? total : k;
 }
 
+// The one-warp part of the draw for at most 64 candidates: pj[j] = exp(v_j - v_0) and acc[j] = exp((v_j - v_0) / T)
+// are in shared memory, the uniform in sc.hist.  Lane 0 walks the running sums left to right, as the reference adds
+// (src/kernels.cu:702-719); every lane then holds candidates j = lane and lane + 32, and the three decisions (top-p
+// cut, min-p cut, inverse-CDF hit) are the first set bits of ballots.  Called by the 32 threads of warp 0.
+__device__ __forceinline__ void draw_warp(const uint64_t * sorted, int nk, double * pj, double * acc, double * qj,
+                                          SelectScratch & sc, const fns_b200_params & p, int32_t * out_token) {
+    const int tid = threadIdx.x;
+    const int lane = tid, hi = tid + 32;
+    double sum = 0.0;
+    if (lane == 0) {
+        double run = 0.0;
+        int j = 0;
+        for (; j + 4 <= nk; j += 4) {
+            double a4[4], w4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                a4[u] = pj[j + u];
+                w4[u] = acc[j + u];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                sum += a4[u];
+                run += w4[u];
+                acc[j + u] = run;
+            }
+        }
+        for (; j < nk; ++j) {
+            sum += pj[j];
+            run += acc[j];
+            acc[j] = run;
+        }
+    }
+    __syncwarp();
+    sum = __shfl_sync(kFull, sum, 0);
+    const double p0 = lane < nk ? pj[lane] : 0.0, p1 = hi < nk ? pj[hi] : 0.0;
+    if (lane < nk) qj[lane] = p0 / sum;
+    if (hi < nk) qj[hi] = p1 / sum;
+    __syncwarp();
+    if (lane == 0) {
+        double run = 0.0;
+        int j = 0;
+        for (; j + 4 <= nk; j += 4) {
+            double q4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) q4[u] = qj[j + u];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                run += q4[u];
+                qj[j + u] = run;
+            }
+        }
+        for (; j < nk; ++j) {
+            run += qj[j];
+            qj[j] = run;
+        }
+    }
+    __syncwarp();
+    auto first_of = [&](bool lo_bit, bool hi_bit, int none) -> int {  // index of the first candidate with the property
+        const uint32_t b0 = __ballot_sync(kFull, lo_bit), b1 = __ballot_sync(kFull, hi_bit);
+        return b0 ? __ffs(b0) - 1 : (b1 ? 31 + __ffs(b1) : none);
+    };
+    const int cut = first_of(lane < nk && qj[lane] >= (double) p.top_p, hi < nk && qj[hi] >= (double) p.top_p, nk - 1) + 1;
+    int keep = cut;
+    if (p.min_p > 0.0f) {
+        const int low = first_of(lane >= 1 && lane < nk && !(p0 >= (double) p.min_p), hi < nk && !(p1 >= (double) p.min_p), nk);
+        keep = low < keep ? low : keep;
+    }
+    const double wsum = acc[keep - 1];
+    const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
+    const int pick = first_of(lane < keep && u < acc[lane], hi < keep && u < acc[hi], keep - 1);
+    if (lane == 0) *out_token = key_id(sorted[pick]);
+}
+
 // The tail of k_sample (src/kernels.cu:698-720) over the nk sorted candidates: candidate softmax, top-p / min-p
 // cut, temperature weights, Philox draw.  exp and the quotients are per-element and run in parallel; the three
 // running sums keep the reference's left-to-right order: `sum` then `cum` on thread 0, the weight prefix (which
@@ -349,70 +423,7 @@ __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double *
         }
         __syncthreads();
         if (tid >= 32) return;
-        const int lane = tid, hi = tid + 32;
-        double sum = 0.0;
-        if (lane == 0) {
-            double run = 0.0;
-            int j = 0;
-            for (; j + 4 <= nk; j += 4) {
-                double a4[4], w4[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    a4[u] = pj[j + u];
-                    w4[u] = acc[j + u];
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    sum += a4[u];
-                    run += w4[u];
-                    acc[j + u] = run;
-                }
-            }
-            for (; j < nk; ++j) {
-                sum += pj[j];
-                run += acc[j];
-                acc[j] = run;
-            }
-        }
-        __syncwarp();
-        sum = __shfl_sync(kFull, sum, 0);
-        const double p0 = lane < nk ? pj[lane] : 0.0, p1 = hi < nk ? pj[hi] : 0.0;
-        if (lane < nk) qj[lane] = p0 / sum;
-        if (hi < nk) qj[hi] = p1 / sum;
-        __syncwarp();
-        if (lane == 0) {
-            double run = 0.0;
-            int j = 0;
-            for (; j + 4 <= nk; j += 4) {
-                double q4[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) q4[u] = qj[j + u];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    run += q4[u];
-                    qj[j + u] = run;
-                }
-            }
-            for (; j < nk; ++j) {
-                run += qj[j];
-                qj[j] = run;
-            }
-        }
-        __syncwarp();
-        auto first_of = [&](bool lo_bit, bool hi_bit, int none) -> int {  // index of the first candidate with the property
-            const uint32_t b0 = __ballot_sync(kFull, lo_bit), b1 = __ballot_sync(kFull, hi_bit);
-            return b0 ? __ffs(b0) - 1 : (b1 ? 31 + __ffs(b1) : none);
-        };
-        const int cut = first_of(lane < nk && qj[lane] >= (double) p.top_p, hi < nk && qj[hi] >= (double) p.top_p, nk - 1) + 1;
-        int keep = cut;
-        if (p.min_p > 0.0f) {
-            const int low = first_of(lane >= 1 && lane < nk && !(p0 >= (double) p.min_p), hi < nk && !(p1 >= (double) p.min_p), nk);
-            keep = low < keep ? low : keep;
-        }
-        const double wsum = acc[keep - 1];
-        const double u = reinterpret_cast<volatile double *>(&sc.hist[0])[1] * wsum;
-        const int pick = first_of(lane < keep && u < acc[lane], hi < keep && u < acc[hi], keep - 1);
-        if (lane == 0) *out_token = key_id(sorted[pick]);
+        draw_warp(sorted, nk, pj, acc, qj, sc, p, out_token);
         return;
     }
     // More candidates (only with k_cap > 64, which the reference does not have: there the summation order is ours to
@@ -1401,7 +1412,127 @@ __global__ void __launch_bounds__(kFinalThreads) k_finalize(const FinalArgs a) {
     // many short lists: witnesses and counting; a few long ones (vocabulary shards): merged pairwise, every key
     // finding its place in the sibling list by a binary search, a merged list keeping its best k
     int nk;
-    if (a.list_len > 64 && k <= a.list_len) {  // (then a merged list is never longer than list_len: the halves fit)
+    if (a.list_len > 64 && a.lists <= 8 && k <= a.list_len) {  // (then a merged run is never longer than list_len: the halves fit)
+        // A few long sorted lists (vocabulary shards).  First a bound: with q = ceil(k / lists), at least k keys reach
+        // the smallest of the lists' q-th keys, so nothing below it can be among the best k - for shards of a
+        // shuffled vocabulary that leaves a fraction of the keys.
+        uint32_t * n_of = &sh.sc.hist[0];  // [lists] keys of a list that reach the bound; [8]: their sum
+        const int L = a.lists, len = a.list_len;
+        if (tid == 0) {
+            const int q = (k + L - 1) / L;
+            uint64_t m = ~0ull;
+            for (int l = 0; l < L; ++l) {
+                const uint64_t key = q - 1 < len ? buf[(size_t) l * len + q - 1] : 0ull;
+                m = key < m ? key : m;
+            }
+            *reinterpret_cast<uint64_t *>(&sh.sc.hist[10]) = m;  // (0: a list is shorter than q keys - no bound)
+        }
+        for (int j = tid; j < a.k_cap; j += kFinalThreads) sorted[j] = 0ull;
+        __syncthreads();
+        const uint64_t m = *reinterpret_cast<const uint64_t *>(&sh.sc.hist[10]);
+        if (tid < L) {  // the keys of list tid that reach the bound (empty slots are 0 and sort last)
+            const uint64_t * lst = buf + (size_t) tid * len;
+            const uint64_t floor_key = m > 1ull ? m : 1ull;
+            int lo = 0, hi = len;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (lst[mid] >= floor_key) lo = mid + 1;
+                else hi = mid;
+            }
+            n_of[tid] = (uint32_t) lo;
+        }
+        __syncthreads();
+        // Then the lists' heads are merged pairwise, level by level: every key finds its place in the merged pair by a
+        // binary search in the sibling run; four keys of a thread search side by side; a merged run keeps its best k.
+        // Run descriptors (start, length, first flat index) live in shared memory, two sets that take turns.
+        uint32_t * desc = &sh.sc.hist[16];  // [2][3][8]: per set the runs' start | length | flat index of the first key
+        uint64_t * spare = reinterpret_cast<uint64_t *>(&sh + 1);  // [(lists + 1) / 2 * list_len + k_cap]
+        if (tid == 0) {
+            uint32_t flat = 0u;
+            for (int l = 0; l < 8; ++l) {
+                desc[l] = (uint32_t) (l * len);
+                desc[8 + l] = l < L ? n_of[l] : 0u;
+                desc[16 + l] = flat;
+                flat += desc[8 + l];
+            }
+            sh.sc.count = flat;
+        }
+        __syncthreads();
+        const int total = (int) sh.sc.count;
+        uint64_t * src = buf, * dst = spare;
+        int runs = L, set = 0, level_total = total;
+#pragma unroll 1
+        while (runs > 1) {
+            const uint32_t * st = desc + set * 24, * nn = st + 8, * first = st + 16;
+            uint32_t * ost = desc + (set ^ 1) * 24, * onn = ost + 8, * ofirst = ost + 16;
+            const int out_runs = (runs + 1) >> 1;
+            if (tid == 0) {  // the next level's runs: side by side at a distance of k
+                uint32_t flat = 0u;
+                for (int r = 0; r < 8; ++r) {
+                    const uint32_t both = r < out_runs ? nn[2 * r] + (2 * r + 1 < runs ? nn[2 * r + 1] : 0u) : 0u;
+                    ost[r] = (uint32_t) (r * k);
+                    onn[r] = both < (uint32_t) k ? both : (uint32_t) k;
+                    ofirst[r] = flat;
+                    flat += onn[r];
+                }
+                sh.sc.count = flat;
+            }
+#pragma unroll 1
+            for (int base = tid; base < level_total; base += 4 * kFinalThreads) {
+                uint64_t key[4];
+                const uint64_t * sib[4];
+                int lo[4], hi[4], at[4], lim[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int idx = base + q * kFinalThreads;
+                    key[q] = 0ull;
+                    sib[q] = src;
+                    lo[q] = hi[q] = at[q] = lim[q] = 0;
+                    if (idx < level_total) {
+                        int r = 0;
+#pragma unroll
+                        for (int t = 1; t < 8; ++t) r += t < runs && (uint32_t) idx >= first[t] ? 1 : 0;
+                        const int i = idx - (int) first[r];
+                        key[q] = src[st[r] + i];
+                        const int other = r ^ 1;
+                        if (other < runs) {
+                            sib[q] = src + st[other];
+                            hi[q] = (int) nn[other];
+                        }
+                        at[q] = (int) ost[r >> 1] + i;
+                        lim[q] = (int) ost[r >> 1] + (int) onn[r >> 1];
+                    }
+                }
+                while (lo[0] < hi[0] || lo[1] < hi[1] || lo[2] < hi[2] || lo[3] < hi[3]) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (lo[q] < hi[q]) {
+                            const int mid = (lo[q] + hi[q]) >> 1;
+                            if (sib[q][mid] > key[q]) lo[q] = mid + 1;
+                            else hi[q] = mid;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (key[q] != 0ull && at[q] + lo[q] < lim[q]) dst[at[q] + lo[q]] = key[q];
+            }
+            __syncthreads();
+            level_total = (int) sh.sc.count;
+            uint64_t * t = src;
+            src = dst;
+            dst = t;
+            runs = out_runs;
+            set ^= 1;
+        }
+        {
+            const uint32_t * st = desc + set * 24, * nn = st + 8;
+            const int have = (int) nn[0];
+            for (int j = tid; j < have && j < k; j += kFinalThreads) sorted[j] = src[st[0] + j];
+        }
+        __syncthreads();
+        nk = total < k ? total : k;
+    } else if (a.list_len > 64 && k <= a.list_len) {  // (then a merged list is never longer than list_len: the halves fit)
         uint64_t * spare = reinterpret_cast<uint64_t *>(&sh + 1);  // [lists * list_len / 2 + k]
         int len = 0;
         const uint64_t * res = merge_runs<kFinalThreads>(buf, spare, a.lists, a.list_len, k, &len);
