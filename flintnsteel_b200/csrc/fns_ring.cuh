@@ -151,46 +151,50 @@ __device__ uint64_t * merge_runs(uint64_t * a, uint64_t * b, int runs, int L, in
     return a;
 }
 
-// The same when the number of runs and their length L = 1 << lg are powers of two (no division, and the four keys a
-// thread takes per round search side by side).
+// C consecutive outputs, d0 .. d0 + C - 1, of the merge of two descending runs A[0 .. na) and B[0 .. nb) (distinct keys;
+// an empty slot is 0 and sorts last): a binary search along the diagonal d0 finds how many of the first d0 outputs come
+// from A, then the outputs are taken one by one.  Outputs at or beyond `limit` are not produced.
+template <int C>
+__device__ __forceinline__ void merge_chunk(const uint64_t * A, int na, const uint64_t * B, int nb, int d0, int limit,
+                                            uint64_t * out) {
+    int lo = d0 - nb > 0 ? d0 - nb : 0, hi = d0 < na ? d0 : na;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (A[mid] > B[d0 - mid - 1]) lo = mid + 1;
+        else hi = mid;
+    }
+    int i = lo, j = d0 - lo;
+    uint64_t x = i < na ? A[i] : 0ull, y = j < nb ? B[j] : 0ull;
+#pragma unroll
+    for (int t = 0; t < C; ++t) {
+        if (d0 + t >= limit) break;
+        const bool from_a = x > y || j >= nb;
+        out[d0 + t] = from_a ? x : y;
+        if (from_a) {
+            ++i;
+            x = i < na ? A[i] : 0ull;
+        } else {
+            ++j;
+            y = j < nb ? B[j] : 0ull;
+        }
+    }
+}
+
+// Merges `runs` sorted runs of 1 << lg keys each (a power of two of them, side by side in a) pairwise until one is
+// left, a merged run keeping its best `keep` keys (a power of two): every thread produces four consecutive keys of a
+// merged run at a time.  a and b alternate as source and destination; returns the buffer that holds the result.
+// All NT threads; block synchronised on entry and exit.
 template <int NT>
-__device__ uint64_t * merge_runs_pow2(uint64_t * a, uint64_t * b, int runs, int lg, int keep) {
+__device__ uint64_t * merge_levels_pow2(uint64_t * a, uint64_t * b, int runs, int lg, int keep) {
     while (runs > 1) {
         const int L = 1 << lg;
-        const bool cut = 2 * L > keep;  // the merged run keeps `keep` keys (a power of two as well, or everything)
-        const int lg_out = cut ? lg : lg + 1;
+        const int lg_out = 2 * L > keep ? lg : lg + 1;  // (a merged run of 2 L keys is cut back to keep = L)
         const int Lout = 1 << lg_out;
-        const int total = runs << lg;
-        for (int i = threadIdx.x; i < (runs >> 1) * Lout; i += NT) b[i] = 0ull;
-        __syncthreads();
-        for (int base = threadIdx.x; base < total; base += 4 * NT) {
-            uint64_t key[4];
-            int lo[4], hi[4];
-            const uint64_t * sib[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int idx = base + q * NT;
-                key[q] = idx < total ? a[idx] : 0ull;
-                sib[q] = a + ((size_t) ((idx >> lg) ^ 1) << lg);
-                lo[q] = 0;
-                hi[q] = key[q] != 0ull ? L : 0;
-            }
-            for (int step = 0; step <= lg; ++step) {  // (at most lg + 1 halvings of [0, L])
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    if (lo[q] < hi[q]) {
-                        const int mid = (lo[q] + hi[q]) >> 1;
-                        if (sib[q][mid] > key[q]) lo[q] = mid + 1;
-                        else hi[q] = mid;
-                    }
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int idx = base + q * NT;
-                const int pos = (idx & (L - 1)) + lo[q];
-                if (key[q] != 0ull && pos < Lout) b[((size_t) (idx >> (lg + 1)) << lg_out) + pos] = key[q];
-            }
+        const int chunks = ((runs >> 1) << lg_out) >> 2;
+        for (int c = threadIdx.x; c < chunks; c += NT) {
+            const int r = (c << 2) >> lg_out, d0 = (c << 2) & (Lout - 1);
+            const uint64_t * A = a + ((size_t) (2 * r) << lg);
+            merge_chunk<4>(A, L, A + L, L, d0, Lout, b + ((size_t) r << lg_out));
         }
         __syncthreads();
         uint64_t * t = a;
@@ -200,71 +204,6 @@ __device__ uint64_t * merge_runs_pow2(uint64_t * a, uint64_t * b, int runs, int 
         lg = lg_out;
     }
     return a;
-}
-
-// Sorts up to NT * KPT keys into descending order with the keys in registers: a bitonic network in which thread t holds
-// elements t * KPT .. t * KPT + KPT - 1.  Exchanges at a distance below KPT stay inside the thread, those below
-// 32 * KPT go through warp shuffles, and only the few steps that pair elements of different warps go through shared
-// memory (one barrier each; two buffers of NT * KPT keys take turns, so a buffer is not written while a slower warp
-// still reads it).  in[0 .. n) are the keys (0 = empty, sorts last); the first `take` keys of the result go to out.
-// in may be x0 (it is read before anything is written).  All NT threads; block synchronised on entry.
-template <int NT, int KPT>
-__device__ void block_sort_regs(const uint64_t * in, int n, uint64_t * x0, uint64_t * x1, uint64_t * out, int take) {
-    static_assert(KPT == 2 || KPT == 4, "two or four keys per thread");
-    constexpr int M = NT * KPT;
-    const int tid = threadIdx.x;
-    uint64_t q[KPT];
-#pragma unroll
-    for (int j = 0; j < KPT; ++j) q[j] = tid * KPT + j < n ? in[tid * KPT + j] : 0ull;
-    __syncthreads();  // (in may be an exchange buffer)
-    auto inside = [&](int i, int j, bool desc) {
-        if ((q[i] < q[j]) == desc) {
-            const uint64_t t = q[i];
-            q[i] = q[j];
-            q[j] = t;
-        }
-    };
-    uint64_t * xb = x0;
-#pragma unroll 1
-    for (int size = 2; size <= M; size <<= 1) {
-#pragma unroll 1
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            const bool desc = ((tid * KPT) & size) == 0;  // (the same for all keys of a thread once size >= KPT; below, see inside)
-            if (stride < KPT) {
-                if (KPT == 2) {
-                    inside(0, 1, desc);
-                } else if (stride == 1) {
-                    inside(0, 1, size == 2 ? true : desc);
-                    inside(2, 3, size == 2 ? false : desc);
-                } else {
-                    inside(0, 2, desc);
-                    inside(1, 3, desc);
-                }
-            } else if (stride < 32 * KPT) {
-                const int lx = stride / KPT;
-                const bool keep_max = (((tid * KPT) & stride) == 0) == desc;
-#pragma unroll
-                for (int j = 0; j < KPT; ++j) {
-                    const uint64_t other = __shfl_xor_sync(kFull, q[j], lx);
-                    q[j] = keep_max ? (other > q[j] ? other : q[j]) : (other < q[j] ? other : q[j]);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < KPT; ++j) xb[tid * KPT + j] = q[j];
-                __syncthreads();
-                const bool keep_max = (((tid * KPT) & stride) == 0) == desc;
-#pragma unroll
-                for (int j = 0; j < KPT; ++j) {
-                    const uint64_t other = xb[(tid * KPT + j) ^ stride];
-                    q[j] = keep_max ? (other > q[j] ? other : q[j]) : (other < q[j] ? other : q[j]);
-                }
-                xb = xb == x0 ? x1 : x0;
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < KPT; ++j)
-        if (tid * KPT + j < take) out[tid * KPT + j] = q[j];
 }
 
 // Sorts a[0 .. m) (m a power of two, in shared memory) into descending order: a bitonic network, one barrier per
@@ -854,10 +793,10 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                 const int n_work = (int) sh.n_vl;
                 listed = n_work <= a.list_cap;  // uniform
                 const int total = listed ? n_work * NVEC : 0;
-                constexpr int PB = 2;  // items per thread whose loads are in flight together
+                constexpr int PB = sizeof(T) == 2 ? 4 : 2;  // items per thread whose loads are in flight together (kept as raw 16-byte words)
 #pragma unroll 1
                 for (int i0 = warp * 32; i0 < total; i0 += PB * NT) {  // (the same rounds for every lane of a warp)
-                    float xv[PB][VEC];
+                    uint4 raw[PB];
                     uint32_t bits[PB], e0[PB];
 #pragma unroll
                     for (int q = 0; q < PB; ++q) {
@@ -869,22 +808,36 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
                             const int v = i % NVEC;
                             bits[q] = ((uint32_t) eff16[cell] >> (v * VEC)) & kVecBits;
                             e0[q] = cell * kCell + (uint32_t) (v * VEC);
-                            if (bits[q]) load_vec<T, VEC>(x + e0[q], xv[q]);
+                            if (bits[q]) raw[q] = __ldg(reinterpret_cast<const uint4 *>(x + e0[q]));
                         }
                     }
 #pragma unroll
                     for (int q = 0; q < PB; ++q) {
                         uint32_t hit = 0u;  // the elements of this vector that reach the bound
+                        float xq[VEC];
                         if (bits[q]) {
+                            if constexpr (sizeof(T) == 4) {
+                                xq[0] = __uint_as_float(raw[q].x);
+                                xq[1] = __uint_as_float(raw[q].y);
+                                xq[2] = __uint_as_float(raw[q].z);
+                                xq[3] = __uint_as_float(raw[q].w);
+                            } else {
+                                const uint32_t w4[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    xq[2 * j] = __uint_as_float(w4[j] << 16);
+                                    xq[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
+                                }
+                            }
 #pragma unroll
                             for (int j = 0; j < VEC; ++j)
-                                hit |= (((bits[q] >> j) & 1u) && xv[q][j] >= thr_v && xv[q][j] <= FLT_MAX) ? 1u << j : 0u;
+                                hit |= (((bits[q] >> j) & 1u) && xq[j] >= thr_v && xq[j] <= FLT_MAX) ? 1u << j : 0u;
                         }
                         if (k == 1) {
 #pragma unroll
                             for (int j = 0; j < VEC; ++j) {
                                 if (!((hit >> j) & 1u)) continue;
-                                const uint64_t key = make_key(xv[q][j], id0 + e0[q] + (uint32_t) j);
+                                const uint64_t key = make_key(xq[j], id0 + e0[q] + (uint32_t) j);
                                 best = key > best ? key : best;
                             }
                             continue;
@@ -903,7 +856,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
 #pragma unroll
                         for (int j = 0; j < VEC; ++j) {
                             if (!((hit >> j) & 1u)) continue;
-                            if (at < (uint32_t) a.cap) buf[at] = make_key(xv[q][j], id0 + e0[q] + (uint32_t) j);
+                            if (at < (uint32_t) a.cap) buf[at] = make_key(xq[j], id0 + e0[q] + (uint32_t) j);
                             ++at;
                         }
                     }
@@ -990,13 +943,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     while (4 * pow2_runs < n) pow2_runs <<= 1;
     if (n <= kRankSelectMax) {
         got = block_rank_select<NT>(buf, n, k, sorted);
-    } else if (n <= 2 * NT && a.cap >= 4 * NT) {
-        // a longer list (k beyond 384): sorted as it is, in registers
-        got = n < k ? n : k;
-        block_sort_regs<NT, 2>(buf, n, buf, buf + 2 * NT, sorted, got);
-    } else if (n <= 4 * NT && a.cap >= 8 * NT) {
-        got = n < k ? n : k;
-        block_sort_regs<NT, 4>(buf, n, buf, buf + 4 * NT, sorted, got);
     } else if (8 * pow2_runs <= a.cap) {
         // a long list (k beyond 384): sorted as it is, by merging.  Every thread orders four keys in registers, the
         // runs of four (a power of two of them: empty runs fill up) are merged pairwise in the two halves of the
@@ -1025,7 +971,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
         __syncthreads();
         int keep = 4;  // a merged run keeps the best `keep` keys: the power of two that holds k
         while (keep < k) keep <<= 1;
-        const uint64_t * res = merge_runs_pow2<NT>(buf, buf + half, runs, 2, keep);
+        const uint64_t * res = merge_levels_pow2<NT>(buf, buf + half, runs, 2, keep);
         got = n < k ? n : k;
         for (int i = tid; i < got; i += NT) sorted[i] = res[i];
     } else {

@@ -1442,83 +1442,53 @@ __global__ void __launch_bounds__(kFinalThreads) k_finalize(const FinalArgs a) {
             n_of[tid] = (uint32_t) lo;
         }
         __syncthreads();
-        // Then the lists' heads are merged pairwise, level by level: every key finds its place in the merged pair by a
-        // binary search in the sibling run; four keys of a thread search side by side; a merged run keeps its best k.
-        // Run descriptors (start, length, first flat index) live in shared memory, two sets that take turns.
-        uint32_t * desc = &sh.sc.hist[16];  // [2][3][8]: per set the runs' start | length | flat index of the first key
+        // Then the lists' heads are merged pairwise, level by level; a merged run keeps its best k; every thread
+        // produces four consecutive keys of a merged run at a time (merge_chunk).  Run descriptors (start, length,
+        // first chunk) live in shared memory, two sets that take turns.
+        uint32_t * desc = &sh.sc.hist[16];  // [2][3][8]: per set the runs' start | length | index of the first chunk
         uint64_t * spare = reinterpret_cast<uint64_t *>(&sh + 1);  // [(lists + 1) / 2 * list_len + k_cap]
         if (tid == 0) {
-            uint32_t flat = 0u;
+            uint32_t all = 0u;
             for (int l = 0; l < 8; ++l) {
                 desc[l] = (uint32_t) (l * len);
                 desc[8 + l] = l < L ? n_of[l] : 0u;
-                desc[16 + l] = flat;
-                flat += desc[8 + l];
+                all += desc[8 + l];
             }
-            sh.sc.count = flat;
+            sh.sc.count = all;
         }
         __syncthreads();
         const int total = (int) sh.sc.count;
         uint64_t * src = buf, * dst = spare;
-        int runs = L, set = 0, level_total = total;
+        int runs = L, set = 0;
 #pragma unroll 1
         while (runs > 1) {
-            const uint32_t * st = desc + set * 24, * nn = st + 8, * first = st + 16;
+            const uint32_t * st = desc + set * 24, * nn = st + 8;
             uint32_t * ost = desc + (set ^ 1) * 24, * onn = ost + 8, * ofirst = ost + 16;
             const int out_runs = (runs + 1) >> 1;
-            if (tid == 0) {  // the next level's runs: side by side at a distance of k
-                uint32_t flat = 0u;
+            if (tid == 0) {  // the merged runs: side by side at a distance of k
+                uint32_t chunks = 0u;
                 for (int r = 0; r < 8; ++r) {
                     const uint32_t both = r < out_runs ? nn[2 * r] + (2 * r + 1 < runs ? nn[2 * r + 1] : 0u) : 0u;
                     ost[r] = (uint32_t) (r * k);
                     onn[r] = both < (uint32_t) k ? both : (uint32_t) k;
-                    ofirst[r] = flat;
-                    flat += onn[r];
+                    ofirst[r] = chunks;
+                    chunks += (onn[r] + 3u) >> 2;
                 }
-                sh.sc.count = flat;
-            }
-#pragma unroll 1
-            for (int base = tid; base < level_total; base += 4 * kFinalThreads) {
-                uint64_t key[4];
-                const uint64_t * sib[4];
-                int lo[4], hi[4], at[4], lim[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int idx = base + q * kFinalThreads;
-                    key[q] = 0ull;
-                    sib[q] = src;
-                    lo[q] = hi[q] = at[q] = lim[q] = 0;
-                    if (idx < level_total) {
-                        int r = 0;
-#pragma unroll
-                        for (int t = 1; t < 8; ++t) r += t < runs && (uint32_t) idx >= first[t] ? 1 : 0;
-                        const int i = idx - (int) first[r];
-                        key[q] = src[st[r] + i];
-                        const int other = r ^ 1;
-                        if (other < runs) {
-                            sib[q] = src + st[other];
-                            hi[q] = (int) nn[other];
-                        }
-                        at[q] = (int) ost[r >> 1] + i;
-                        lim[q] = (int) ost[r >> 1] + (int) onn[r >> 1];
-                    }
-                }
-                while (lo[0] < hi[0] || lo[1] < hi[1] || lo[2] < hi[2] || lo[3] < hi[3]) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        if (lo[q] < hi[q]) {
-                            const int mid = (lo[q] + hi[q]) >> 1;
-                            if (sib[q][mid] > key[q]) lo[q] = mid + 1;
-                            else hi[q] = mid;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    if (key[q] != 0ull && at[q] + lo[q] < lim[q]) dst[at[q] + lo[q]] = key[q];
+                sh.sc.bucket = chunks;
             }
             __syncthreads();
-            level_total = (int) sh.sc.count;
+            const int chunks = (int) sh.sc.bucket;
+#pragma unroll 1
+            for (int c = tid; c < chunks; c += kFinalThreads) {
+                int r = 0;
+#pragma unroll
+                for (int t = 1; t < 4; ++t) r += t < out_runs && (uint32_t) c >= ofirst[t] ? 1 : 0;
+                const int d0 = (c - (int) ofirst[r]) << 2;
+                const bool pair = 2 * r + 1 < runs;
+                merge_chunk<4>(src + st[2 * r], (int) nn[2 * r], src + (pair ? st[2 * r + 1] : 0u), pair ? (int) nn[2 * r + 1] : 0, d0,
+                               (int) onn[r], dst + ost[r]);
+            }
+            __syncthreads();
             uint64_t * t = src;
             src = dst;
             dst = t;

@@ -554,6 +554,48 @@ def test_vocab_shards_merge_to_the_unsharded_answer(dev, oracle, shards):
     check_against_oracle(oracle, w, out.cpu().numpy(), cands_to_numpy(merged))
 
 
+@pytest.mark.parametrize("shards", [2, 8])
+def test_vocab_shards_that_are_nothing_alike(dev, oracle, shards):
+    """The merge prunes the lists by the smallest of their (k / lists)-th keys before it merges them.  Rows whose
+    best keys all sit in one shard, whose other shards hold a handful of allowed ids or none, small k and greedy
+    rows must come out as the unsharded call gives them."""
+    w = wl.large_vocab(seed=4, rows=6)
+    step = w.vocab // shards
+    x = wl.bf16_bits_to_f32(w.logits)
+    x[0, :step] += np.float32(20.0)                      # every candidate of row 0 comes from shard 0
+    masks = w.masks.copy()
+    words = step // 32
+    masks[1, words:2 * words] = 0
+    masks[1, words] = np.uint32(0x0000ffff)              # shard 1 of row 1: sixteen allowed ids
+    masks[2, words:] = 0                                 # row 2: only shard 0 has allowed ids
+    masks[5, :] = 0
+    masks[5, ::27] = np.uint32(0x00010000)               # row 5: about 300 allowed ids in all
+    p = w.params.copy()
+    p["top_k"][3] = 5
+    p["temperature"][4] = 0.0
+    w2 = wl.Workload("skewed_shards", wl.f32_to_bf16_bits(x), p, masks, None, None, bf16=True, k_cap=1024)
+    lg, mk, _, _ = upload(w2, dev)
+    pd = params_to_device(p, dev)
+    s = Sampler(0, max_rows=6, max_vocab=w.vocab, k_cap=1024)
+    full = cands_tensor(6, 1024, dev)
+    s.select_rows(lg, pd, full, masks=mk)
+    parts = []
+    for g in range(shards):
+        part = cands_tensor(6, 1024, dev)
+        s.select_rows(lg[:, g * step:(g + 1) * step], pd, part, id_base=g * step, masks=mk[:, g * words:(g + 1) * words], vocab=step)
+        parts.append(part)
+    gathered = torch.stack(parts, dim=1).contiguous()
+    out = torch.empty(6, dtype=torch.int32, device=dev)
+    merged = cands_tensor(6, 1024, dev)
+    s.finalize_rows(gathered, shards, 1024, 6, pd, out_tokens=out, out_cands=merged)
+    direct = torch.empty(6, dtype=torch.int32, device=dev)
+    s.sample_rows(lg, pd, direct, masks=mk)
+    torch.cuda.synchronize()
+    s.device_status()
+    assert torch.equal(merged, full) and torch.equal(out, direct)
+    check_against_oracle(oracle, w2, out.cpu().numpy(), cands_to_numpy(merged))
+
+
 # ---- error behaviour ---------------------------------------------------------------------------------------
 def test_capacity_and_argument_errors(dev):
     s = Sampler(0, max_rows=2, max_vocab=1000, k_cap=64, max_history=16)
