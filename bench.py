@@ -121,6 +121,24 @@ def run_b200(args):
     dev = torch.device(f"cuda:{local}")
     rows, K, W = args.rows, args.steps, args.warmup
 
+    if args.only_batch1:  # profiler runs of the few-row kernel: ten plain launches per case and nothing else
+        res = {}
+        cases = {"single_row_T0.7": wl.single_row(), "single_row_greedy": wl.single_row(greedy=True), "grammar_row": wl.grammar_row()}
+        for name, w in cases.items():
+            s = Sampler(local, max_rows=1, max_vocab=w.vocab, k_cap=64, max_history=4096)
+            lg = torch.from_numpy(w.logits).to(dev)
+            masks = None if w.masks is None else torch.from_numpy(w.masks.view(np.int32)).to(dev)
+            hist, hl = torch.from_numpy(w.history).to(dev), torch.from_numpy(w.history_len).to(dev)
+            pd = params_to_device(w.params, dev)
+            out1 = torch.empty(1, dtype=torch.int32, device=dev)
+            for _ in range(10):
+                s.sample_rows(lg, pd, out1, masks=masks, history=hist, history_len=hl)
+            torch.cuda.synchronize()
+            s.device_status()
+            res[name] = int(out1.item())
+            s.close()
+        print(json.dumps({"note": "--only-batch1: a profiler run, not a benchmark line", "tokens": res}))
+        return
     # ---- inputs: `batches` distinct 256-row batches per rank, resident in HBM --------------------------------
     host = [wl.session_batch(seed=1000 * rank + b, rows=rows) for b in range(args.batches)]
     vocab = host[0].vocab
@@ -648,6 +666,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--skip-extras", action="store_true", help="no batch-1 / CPU / reference-kernel legs")
     ap.add_argument("--only-headline", action="store_true", help="the timed regions only (for profiler runs)")
+    ap.add_argument("--only-batch1", action="store_true", help="ten launches of each one-row case only (for profiler runs)")
     ap.add_argument("--no-masks", action="store_true", help="every id allowed: the HBM-bound variant of the workload")
     ap.add_argument("--traffic", type=float, default=None,
                     help="dram bytes per select launch from an ncu capture (see profiles/), echoed into the line")

@@ -1751,10 +1751,8 @@ template <typename T, int VEC>
 cudaError_t opt_in_select() {
     cudaError_t e = opt_in(k_select<T, VEC, 512, false>, 200 * 1024);
     if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 512, true>, 200 * 1024);
-#ifndef FNS_DEV_FAST
     if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 256, false>, 200 * 1024);
     if (e == cudaSuccess) e = opt_in(k_select<T, VEC, 256, true>, 200 * 1024);
-#endif
     return e;
 }
 
@@ -1768,11 +1766,9 @@ cudaError_t configure_kernels_once() {  // call with the device current
     std::lock_guard<std::mutex> hold(lock);
     if (configured[dev]) return cudaSuccess;
     e = opt_in_select<float, 4>();
-#ifndef FNS_DEV_FAST
     if (e == cudaSuccess) e = opt_in_select<float, 1>();
     if (e == cudaSuccess) e = opt_in_select<__nv_bfloat16, 8>();
     if (e == cudaSuccess) e = opt_in_select<__nv_bfloat16, 1>();
-#endif
     if (e == cudaSuccess) e = opt_in(k_ring<float>, 226 * 1024);
     if (e == cudaSuccess) e = opt_in(k_ring<__nv_bfloat16>, 226 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_ring<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -1810,7 +1806,6 @@ cudaError_t launch_select_t(const SelectArgs & a, int rows, size_t smem, cudaStr
                                                 : launch_select_d<T, VEC, NT, false>(a, rows, smem, st);
 }
 
-#ifndef FNS_DEV_FAST
 template <int NT>
 cudaError_t launch_select_nt(const SelectArgs & a, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
     if (dtype == FNS_B200_BF16)
@@ -1818,15 +1813,10 @@ cudaError_t launch_select_nt(const SelectArgs & a, int dtype, int vec, int rows,
                         : launch_select_t<__nv_bfloat16, 1, NT>(a, rows, smem, st);
     return vec == 4 ? launch_select_t<float, 4, NT>(a, rows, smem, st) : launch_select_t<float, 1, NT>(a, rows, smem, st);
 }
-#endif
 
 cudaError_t launch_select(const SelectArgs & a, int threads, int dtype, int vec, int rows, size_t smem, cudaStream_t st) {
-#ifdef FNS_DEV_FAST  // development builds: one instantiation only
-    return launch_select_t<float, 4, 512>(a, rows, smem, st);
-#else
     return threads == 512 ? launch_select_nt<512>(a, dtype, vec, rows, smem, st)
                           : launch_select_nt<256>(a, dtype, vec, rows, smem, st);
-#endif
 }
 
 template <typename T>
