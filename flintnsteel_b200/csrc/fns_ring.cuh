@@ -18,13 +18,15 @@
 //            thread's own maximum in a register.  No flags, no running bound, no block barrier inside the loop:
 //            taking candidates on the spot under a running bound was measured and is slower (the insertions
 //            diverge inside the loop that feeds the ring).
-//   bound    k <= 512: (nearly) the k-th largest thread maximum, found by counting; larger k: the k-th largest of
-//            the threads' three best cell maxima, found the same way
+//   bound    k <= 512: (nearly) the k-th largest thread maximum, found by one warp that holds sixteen maxima per lane
+//            and decides two bits per step; larger k: the k-th largest of the threads' three best cell maxima, found
+//            by counting with one block barrier per bit
 //   pass 2   the cells that reach the bound (about k of them) are read again from L2 / HBM, element by element,
 //            and the keys that reach the bound go to the candidate buffer together with the penalised history ids;
 //            if equal values overflow the list or the buffer, every cell is offered again with votes and
 //            compaction, so any input is handled exactly
-//   select   the best k in the total order, then the draw (draw_tail)
+//   select   the best k in the total order (up to 384 keys ranked by counting, more sorted by merging: runs of four
+//            ordered in registers, then merge-path levels), then the draw (draw_tail)
 #pragma once
 
 namespace fnsb {
@@ -480,37 +482,6 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     float tmax = -INFINITY;     // this thread's maximum so far
     uint64_t best = 0ull;       // k == 1: this thread's best key
     bool gave_up = false;
-    const int r_need = (k + kWarps - 1) / kWarps;  // lanes per warp that must hold a value above a bound
-    int lanes_per_group = 32;                      // 32 / (r_need rounded up to a power of two)
-    while (lanes_per_group > 1 && (32 / lanes_per_group) < r_need) lanes_per_group >>= 1;
-    // The bound from the threads' maxima (every thread of the block calls it at the same point): first what the
-    // lane groups of every warp have reached, then tightened to (nearly) the k-th largest thread maximum by a
-    // counted search, bit by bit below the first bit in which that bound and the block's maximum differ.
-    auto bound_from_maxima = [&](float floor_v) -> float {
-        const uint32_t wt = tmax > -INFINITY ? order_word(tmax) : 0u;
-        const uint32_t top = __reduce_max_sync(kFull, wt);
-        if (lane == 0) sh.warp_top[warp] = top;
-        float b = block_bound<NT>(tmax, floor_v, lanes_per_group, true, k == 1, sh);  // (its barrier also covers warp_top)
-        if (k > 1) {
-            uint32_t hi_w = sh.warp_top[0];
-#pragma unroll
-            for (int w = 1; w < kWarps; ++w) hi_w = max(hi_w, sh.warp_top[w]);
-            const uint32_t lo_w = order_word(b);
-            if (hi_w > lo_w) {
-                const int split = 31 - __clz((int) (lo_w ^ hi_w));
-                uint32_t bw = split == 31 ? 0u : (lo_w & ~((2u << split) - 1u));  // the common prefix: <= lo_w, so valid
-                const int stop = split > 10 ? split - 10 : 0;
-#pragma unroll 1
-                for (int bit = split; bit >= stop; --bit) {
-                    const uint32_t cand = bw | (1u << bit);
-                    if (__syncthreads_count(wt >= cand) >= k) bw = cand;
-                }
-                if (bw > lo_w) b = word_value(bw);
-            }
-        }
-        __syncthreads();  // warp_bound / warp_top may be written again
-        return b + 0.0f;  // -0.0 -> +0.0: one key pattern for both zeros
-    };
     {
         const int f = (lane >> (NVEC == 4 ? 1 : 2)) & (NVEC - 1);  // the order in which a lane takes its vectors: no bank conflicts
         // The cell of this thread in the slot: its maximum over the allowed, finite elements (-inf if none).
@@ -625,7 +596,69 @@ __global__ void __launch_bounds__(kRingThreads, 2) k_ring(const SelectArgs a) {
     // 4. The bound: a value that at least k allowed, unpenalised elements reach.
     float thr_v = -FLT_MAX;
     if (k <= NT) {
-        thr_v = bound_from_maxima(-FLT_MAX);
+        // The k-th largest of the threads' maxima (k == 1: the largest).  One warp does it without block barriers:
+        // every lane takes sixteen maxima, the bits in which they differ are found first, and the search decides up
+        // to 14 bits from the highest of them downwards, two bits per step with three warp-wide counts that do not
+        // wait for one another; it stops early once at most four maxima too many remain.
+        uint32_t * wtop = vlist;  // [NT] (the work list is filled later)
+        wtop[tid] = tmax > -INFINITY ? order_word(tmax) : 0u;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t w[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(&wtop[lane * 16 + q * 4]);
+                w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+            }
+            uint32_t wo = 0u, wa = 0xffffffffu, have = 0u, top1 = 0u;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                if (w[q] != 0u) {
+                    wo |= w[q];
+                    wa &= w[q];
+                    ++have;
+                }
+                top1 = max(top1, w[q]);
+            }
+            wo = __reduce_or_sync(kFull, wo);
+            wa = __reduce_and_sync(kFull, wa);
+            have = __reduce_add_sync(kFull, have);
+            uint32_t bw = 0u;
+            if (k == 1) {
+                bw = __reduce_max_sync(kFull, top1);
+            } else if (have >= (uint32_t) k) {  // else: fewer than k threads have seen anything, no bound
+                const uint32_t varying = wo & ~wa;
+                bw = varying ? (wa & ~((2u << (31 - __clz((int) varying))) - 1u)) : wa;  // the common prefix: a valid bound
+                if (varying) {
+                    const int top = 31 - __clz((int) varying);
+                    const int stop = top > 13 ? top - 13 : 0;
+#pragma unroll 1
+                    for (int bit = top; bit >= stop; bit -= 2) {
+                        const uint32_t b1 = 1u << bit, b0 = bit > stop ? 1u << (bit - 1) : 0u;
+                        uint32_t c1 = 0u, c10 = 0u, c0 = 0u;
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) {
+                            c1 += w[q] >= (bw | b1) ? 1u : 0u;
+                            c10 += w[q] >= (bw | b1 | b0) ? 1u : 0u;
+                            c0 += w[q] >= (bw | b0) ? 1u : 0u;
+                        }
+                        c1 = __reduce_add_sync(kFull, c1);
+                        c10 = __reduce_add_sync(kFull, c10);
+                        c0 = __reduce_add_sync(kFull, c0);
+                        uint32_t tot = 0xffffffffu;
+                        if (c10 >= (uint32_t) k) bw |= b1 | b0, tot = c10;
+                        else if (c1 >= (uint32_t) k) bw |= b1, tot = c1;
+                        else if (c0 >= (uint32_t) k) bw |= b0, tot = c0;
+                        if (tot <= (uint32_t) k + 4u) break;
+                    }
+                }
+            }
+            if (lane == 0) sh.warp_top[0] = bw;
+        }
+        __syncthreads();
+        const uint32_t bw = sh.warp_top[0];
+        if (bw != 0u) thr_v = word_value(bw) + 0.0f;  // (-0.0 -> +0.0: one key pattern for both zeros)
+        __syncthreads();  // (the work list's words are written next)
     } else {
         static_assert(FNS_B200_MAX_K <= 3 * NT, "three witnesses per thread cover the largest k");
         const uint32_t b = block_kth_witness<NT>(cmax, n_stages, k, sh.sc);
