@@ -154,7 +154,9 @@ int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, i
  *   cands        entry j of list l of row r is cands[r * row_stride + l * list_stride + j] (strides in entries);
  *                lists * list_len <= 8192.  [rows][lists][list_len] is (row_stride = lists * list_len,
  *                list_stride = list_len); an all-gather of per-shard [rows][k_cap] blocks is
- *                (row_stride = k_cap, list_stride = rows * k_cap)
+ *                (row_stride = k_cap, list_stride = rows * k_cap).  Lists of more than 64 entries must be what
+ *                fns_b200_select_rows writes: descending in the total order, empty entries last, no key in two
+ *                lists (shards do not overlap); shorter lists may come in any order
  *   out_cands    NULL, or [rows][k_cap]: the merged list, for inspection */
 int fns_b200_finalize_rows(fns_b200_sampler * s, const fns_b200_cand * cands, int lists, int list_len,
                            int64_t list_stride, int64_t row_stride, int rows, const fns_b200_params * params,
