@@ -440,6 +440,34 @@ def batch1_latency(torch, dev, local):
         res[name] = {"us_per_row_graph": graph_us, "us_per_row_stream": a.elapsed_time(b) * 1e3 / 200,
                      "bytes_per_row": w.row_bytes(), "plan": s.plan(0, w.vocab, 1, w.history.shape[1])}
         s.close()
+    # a small batch: 8 sessions of the headline workload (masks, 2,048-id histories, all penalties) in one call
+    w = wl.session_batch(seed=77, rows=8)
+    s = Sampler(local, max_rows=8, max_vocab=w.vocab, k_cap=64, max_history=w.history.shape[1])
+    lg, mk = torch.from_numpy(w.logits).to(dev), torch.from_numpy(w.masks.view(np.int32)).to(dev)
+    hist, hl = torch.from_numpy(w.history).to(dev), torch.from_numpy(w.history_len).to(dev)
+    pd = params_to_device(w.params, dev)
+    out8 = torch.empty(8, dtype=torch.int32, device=dev)
+    for _ in range(5):
+        s.sample_rows(lg, pd, out8, masks=mk, history=hist, history_len=hl)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(50):
+                s.sample_rows(lg, pd, out8, masks=mk, history=hist, history_len=hl)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(40):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    res["sessions8_masked_penalised"] = {"us_per_call_graph": a.elapsed_time(b) * 1e3 / (40 * 50), "rows": 8,
+                                         "plan": s.plan(0, w.vocab, 8, w.history.shape[1])}
+    s.close()
     # config 3: one verification window (3 draft positions + bonus = 4 rows), greedy, accept length on the device
     sw = wl.spec_windows(seed=1, windows=1, n_draft=3)
     s = Sampler(local, max_rows=4, max_vocab=sw.vocab, k_cap=64, max_history=0)

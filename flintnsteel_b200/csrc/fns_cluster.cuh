@@ -1,4 +1,5 @@
-// fns_cluster.cuh - k_cluster: the select + draw kernel for one to four rows (launch-to-token latency).
+// fns_cluster.cuh - k_cluster: the select + draw kernel for small batches (launch-to-token latency): as many rows as
+// the device holds clusters at once, and without masks twice that.
 // Included by fns_sampler.cu after the shared helpers (push, compact, draw_tail, merge_lists, ...).
 //
 // One thread-block cluster of 16 CTAs per row; a CTA owns one sixteenth of the row.  The slice comes into shared
@@ -468,9 +469,24 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
         }
         __syncthreads();
         // every CTA has its own region of CTA 0's buffer: plain remote stores, no reservation, no round trip
-        const uint32_t n_loc = sh.n_cand;
-        if (tid == 0) cs0->region_n[rank] = n_loc;  // (more than a region holds: the careful way follows)
-        for (uint32_t i = tid; i < n_loc && i < (uint32_t) kClusterRegion; i += NT) gbuf0[(size_t) rank * kClusterRegion + i] = lbuf[i];
+        uint32_t n_loc = sh.n_cand;
+        const uint64_t * src = lbuf;
+        if (n_loc > (uint32_t) kClusterRegion && n_loc <= (uint32_t) kClusterLocal) {
+            // More than a region holds, but all of it is here (a sparse mask leaves too few witnesses for a bound, and
+            // its allowed ids may all lie in one slice): only this CTA's best k can matter, and k fits a region.
+            int got;
+            if (n_loc <= (uint32_t) kRankSelectMax) {
+                got = block_rank_select<NT>(lbuf, (int) n_loc, k, lsel);
+            } else {
+                const uint64_t tau = block_kth_key<NT>(lbuf, (int) n_loc, k, sh.sc);
+                got = block_take<NT>(lbuf, (int) n_loc, k, tau, lsel, sh.sc);
+            }
+            __syncthreads();
+            n_loc = (uint32_t) got;
+            src = lsel;
+        }
+        if (tid == 0) cs0->region_n[rank] = n_loc;  // (still more than a region holds: the careful way follows)
+        for (uint32_t i = tid; i < n_loc && i < (uint32_t) kClusterRegion; i += NT) gbuf0[(size_t) rank * kClusterRegion + i] = src[i];
         __syncthreads();
         if (tid == 0) sh.n_cand = 0u;  // (the careful way starts from an empty buffer)
     }

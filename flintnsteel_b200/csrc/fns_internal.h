@@ -21,6 +21,8 @@ int fns_b200_set_slices(fns_b200_sampler * s, int slices);
 /* Overrides the block size of the select kernel: 256 (sliced rows), 512 (one block per row when it fits), 0 =
  * automatic.  For the same tests. */
 int fns_b200_set_threads(fns_b200_sampler * s, int threads);
+/* Calls of up to `rows` rows take the cluster kernel (0: never).  For the same tests. */
+int fns_b200_set_cluster_rows(fns_b200_sampler * s, int rows);
 
 /* The engine glue says that the logits of the handle's next calls lie in page-locked HOST memory (on = 1) or in
  * device memory (on = 0): host logits are read in place by the kernel that skips every vector the mask excludes,

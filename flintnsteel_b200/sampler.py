@@ -98,7 +98,7 @@ SYMBOLS = [
 ]
 
 #: exported for the tests, the benchmark and the engine glue only (csrc/fns_internal.h)
-INTERNAL_SYMBOLS = ["fns_b200_plan", "fns_b200_set_slices", "fns_b200_set_threads", "fns_b200_hint_host_logits",
+INTERNAL_SYMBOLS = ["fns_b200_plan", "fns_b200_set_slices", "fns_b200_set_threads", "fns_b200_set_cluster_rows", "fns_b200_hint_host_logits",
                     "fns_b200_mg_create_with_ops"]
 
 _lib = None
@@ -154,6 +154,7 @@ def load_library() -> ctypes.CDLL:
     lib.fns_b200_plan.argtypes = [vp, i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.fns_b200_set_slices.argtypes = [vp, i32]
     lib.fns_b200_set_threads.argtypes = [vp, i32]
+    lib.fns_b200_set_cluster_rows.argtypes = [vp, i32]
     lib.fns_b200_launch_count.argtypes = [vp]
     lib.fns_b200_profile_begin.argtypes = [vp, i32]
     lib.fns_b200_profile_end.argtypes = [vp, vp, f64p, f64p, ctypes.POINTER(i32)]
@@ -270,6 +271,9 @@ class Sampler:
 
     def set_slices(self, slices: int):
         self._check(self.lib.fns_b200_set_slices(self.handle, slices))
+
+    def set_cluster_rows(self, rows: int):
+        self._check(self.lib.fns_b200_set_cluster_rows(self.handle, rows))
 
     def set_threads(self, threads: int):
         self._check(self.lib.fns_b200_set_threads(self.handle, threads))

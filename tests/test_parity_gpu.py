@@ -44,11 +44,15 @@ def upload(w, dev):
     return lg, masks, hist, hl
 
 
-def run_rows(w, dev, k_cap=None, slices=0, max_history=4096):
+def run_rows(w, dev, k_cap=None, slices=0, max_history=4096, cluster_rows=None):
+    """cluster_rows: None = the library's own choice of kernel for the row count; 0 = never the cluster kernel; n = the
+    cluster kernel for calls of up to n rows."""
     k_cap = k_cap or w.k_cap
     s = Sampler(0, max_rows=w.rows, max_vocab=w.vocab, k_cap=k_cap, max_history=max_history)
     if slices:
         s.set_slices(slices)
+    if cluster_rows is not None:
+        s.set_cluster_rows(cluster_rows)
     lg, masks, hist, hl = upload(w, dev)
     pd = params_to_device(w.params, dev)
     out = torch.full((w.rows,), -7, dtype=torch.int32, device=dev)

@@ -1,8 +1,9 @@
-"""The bulk-copy kernel (k_ring) against the oracle on the inputs that stress it.
+"""The bulk-copy kernel (k_ring) and the cluster kernel (k_cluster) against the oracle on the inputs that stress them.
 
-Whole-row calls take k_ring when they have no mask, and always when k_cap exceeds 512 (then also under a mask), so the
-cases below pick k_cap and masks accordingly.  Everything goes through the C ABI; candidates must be bit-exact and
-tokens equal (or on a CDF boundary within 1e-6), as in test_parity_gpu.py.
+Calls of many rows take k_ring when they have no mask, and always when k_cap exceeds 512 (then also under a mask);
+small batches with k_cap up to 128 take k_cluster.  The cases below pick k_cap and masks accordingly and say which
+kernel a small batch is meant for (run_rows' cluster_rows).  Everything goes through the C ABI; candidates must be
+bit-exact and tokens equal (or on a CDF boundary within 1e-6), as in test_parity_gpu.py.
 """
 import numpy as np
 import pytest
@@ -38,7 +39,8 @@ def test_ragged_vocabularies_masked_and_unmasked(dev, oracle, n, bf16):
     assert tokens[0] == -1 and tokens[1] == n - 1
     check_against_oracle(oracle, w, tokens, cands)
     w2 = wl.Workload("ragged_unmasked", logits, p, None, hist, hl, bf16=bf16, k_cap=64)
-    check_against_oracle(oracle, w2, *run_rows(w2, dev, max_history=64))
+    check_against_oracle(oracle, w2, *run_rows(w2, dev, max_history=64, cluster_rows=0))   # k_ring
+    check_against_oracle(oracle, w2, *run_rows(w2, dev, max_history=64, cluster_rows=6))   # six clusters
 
 
 def test_equal_values_take_the_careful_walk(dev, oracle):
@@ -59,15 +61,17 @@ def test_equal_values_take_the_careful_walk(dev, oracle):
         p = make_params(6, temperature=temperature, top_k=64, top_p=0.99, repetition=1.2, presence=0.4, frequency=0.01,
                         seed=11)
         w = wl.Workload("equal", x, p, None, hist, hl)
-        tokens, cands = run_rows(w, dev)
-        check_against_oracle(oracle, w, tokens, cands)
-        if temperature == 0.0:
-            assert tokens[1] == 0  # no history: the first of all the equal values
+        for cluster_rows in (0, 6):  # k_ring, and six clusters
+            tokens, cands = run_rows(w, dev, cluster_rows=cluster_rows)
+            check_against_oracle(oracle, w, tokens, cands)
+            if temperature == 0.0:
+                assert tokens[1] == 0  # no history: the first of all the equal values
     # the same rows under masks go through k_select: a greedy row whose work list overflows takes its careful walk
     masks = np.stack([wl.run_mask(wl.rng(3 + r), n, 0.7, 20) for r in range(6)])
     p = make_params(6, temperature=0.0, repetition=1.2, presence=0.4, frequency=0.01)
     w = wl.Workload("equal_masked", x, p, masks, hist, hl)
-    check_against_oracle(oracle, w, *run_rows(w, dev))
+    check_against_oracle(oracle, w, *run_rows(w, dev, cluster_rows=0))
+    check_against_oracle(oracle, w, *run_rows(w, dev, cluster_rows=6))
 
 
 def test_more_owned_history_ids_than_the_registers_hold(dev, oracle):
@@ -85,7 +89,8 @@ def test_more_owned_history_ids_than_the_registers_hold(dev, oracle):
     p["temperature"][0] = 0.0
     p["frequency"][3] = -0.1
     w = wl.Workload("many_owned", x, p, None, hist, np.full(rows, h, np.int32))
-    check_against_oracle(oracle, w, *run_rows(w, dev, max_history=h))
+    check_against_oracle(oracle, w, *run_rows(w, dev, max_history=h, cluster_rows=0))
+    check_against_oracle(oracle, w, *run_rows(w, dev, max_history=h, cluster_rows=6))
 
 
 @pytest.mark.parametrize("k", [513, 700, 1024])
@@ -121,9 +126,10 @@ def test_special_values_in_whole_rows(dev, oracle):
     p = make_params(6, temperature=1.0, top_k=8)
     p["temperature"][:5] = 0.0
     w = wl.Workload("special", x, p)
-    tokens, cands = run_rows(w, dev)
-    assert list(tokens[:5]) == [100_000, 150_077, 90_005, 0, -1]
-    check_against_oracle(oracle, w, tokens, cands)
+    for cluster_rows in (0, 6):  # k_ring, and six clusters
+        tokens, cands = run_rows(w, dev, cluster_rows=cluster_rows)
+        assert list(tokens[:5]) == [100_000, 150_077, 90_005, 0, -1]
+        check_against_oracle(oracle, w, tokens, cands)
 
 
 # ---- one to four rows: the cluster kernel (16 CTAs per row, candidates meet in distributed shared memory) -----------
@@ -164,6 +170,26 @@ def test_few_rows_with_equal_values_and_hot_histories(dev, oracle):
         p["frequency"][3] = -0.05  # more occurrences raise the value: every owned id needs its count
         w = wl.Workload("few_equal", x, p, None, hist, hl)
         check_against_oracle(oracle, w, *run_rows(w, dev, max_history=6000))
+
+
+def test_few_rows_under_masks_that_leave_no_bound(dev, oracle):
+    """A mask that allows a few hundred ids, all in one or two slices: too few witnesses for a bound, so every allowed
+    id is a candidate, and the CTA that holds them all sends only its own best k."""
+    n = 151_936
+    g = wl.rng(123)
+    rows = 10
+    x = wl.gaussian_logits(g, rows, n, 2.5)
+    masks = np.zeros((rows, (n + 31) // 32), np.uint32)
+    for r in range(rows):
+        start = int(g.integers(0, n - 4000))
+        ids = start + np.sort(g.choice(3000, size=(30, 130, 200, 600, 1500)[r % 5], replace=False))
+        np.bitwise_or.at(masks[r], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+    hist = g.integers(0, n, size=(rows, 256), dtype=np.int32)
+    p = make_params(rows, temperature=0.8, top_k=64, top_p=0.97, repetition=1.1, presence=0.2, frequency=0.1, seed=9)
+    p["temperature"][::3] = 0.0
+    w = wl.Workload("no_bound", x, p, masks, hist, np.full(rows, 256, np.int32))
+    check_against_oracle(oracle, w, *run_rows(w, dev, max_history=256, cluster_rows=12))
+    check_against_oracle(oracle, w, *run_rows(w, dev, max_history=256, cluster_rows=0))
 
 
 def test_one_verification_window_of_four_columns(dev, oracle):
