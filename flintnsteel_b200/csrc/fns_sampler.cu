@@ -239,79 +239,6 @@ __device__ int merge_lists(uint64_t * buf, int lists, int len, uint64_t * sel, u
     return nk;
 }
 
-// The same merge for long lists (vocabulary shards: a few lists of up to 1,024 keys): every key finds its place in
-// the merged order directly.  Its rank is its position in its own list plus, for every other list, the number of
-// keys there that are larger - a binary search, since the lists are sorted; keys are distinct, so ranks are too,
-// and a key of rank < k goes straight to sorted[rank].  A thread takes up to MAXC consecutive keys of one list:
-// their positions in another list only move forward, so after the first search the rest gallop from where the
-// previous one ended.  Only the first min(len, k) keys of a list can be among the best k.  No scratch, two barriers.
-// Returns the number of candidates; sorted[nk .. k_cap) = 0.  All NT threads; block synchronised on entry and exit.
-template <int NT, int MAXC>
-__device__ int merge_ranked(const uint64_t * buf, int lists, int len, uint64_t * sorted, SelectScratch & sc, int k, int k_cap) {
-    const int tid = threadIdx.x;
-    const int m = len < k ? len : k;
-    for (int j = tid; j < k_cap; j += NT) sorted[j] = 0ull;
-    if (tid == 0) sc.count = 0u;
-    __syncthreads();
-    for (int l = tid; l < lists; l += NT) {  // how many candidates there are at all (empty slots sit at the end)
-        const uint64_t * a = buf + (size_t) l * len;
-        int lo = 0, hi = m;
-        while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            if (a[mid] != 0ull) lo = mid + 1;
-            else hi = mid;
-        }
-        if (lo) atomicAdd(&sc.count, (uint32_t) lo);
-    }
-    int chunk = (lists * m + NT - 1) / NT;
-    chunk = chunk < 1 ? 1 : (chunk > MAXC ? MAXC : chunk);
-    const int per_list = (m + chunk - 1) / chunk;
-    for (int c = tid; c < lists * per_list; c += NT) {
-        const int l = c / per_list, j0 = (c - l * per_list) * chunk;
-        const uint64_t * mine = buf + (size_t) l * len;
-        const int n_e = chunk < m - j0 ? chunk : m - j0;
-        uint64_t x[MAXC];
-        int rank[MAXC];
-#pragma unroll
-        for (int e = 0; e < MAXC; ++e) {
-            x[e] = e < n_e ? mine[j0 + e] : 0ull;
-            rank[e] = j0 + e;
-        }
-        if (x[0] == 0ull) continue;  // sorted, empty slots last: the whole chunk is empty
-        for (int l2 = 0; l2 < lists; ++l2) {
-            if (l2 == l) continue;
-            const uint64_t * other = buf + (size_t) l2 * len;
-            int pos = 0;  // keys of `other` larger than the key at hand
-#pragma unroll
-            for (int e = 0; e < MAXC; ++e) {
-                if (x[e] == 0ull) continue;
-                int lo = pos, hi = m;
-                if (e > 0) {  // gallop: the answer is seldom far from the previous one
-                    int step = 1;
-                    while (lo + step <= m && other[lo + step - 1] > x[e]) {
-                        lo += step;
-                        step <<= 1;
-                    }
-                    hi = lo + step - 1 < m ? lo + step - 1 : m;
-                }
-                while (lo < hi) {
-                    const int mid = (lo + hi) >> 1;
-                    if (other[mid] > x[e]) lo = mid + 1;
-                    else hi = mid;
-                }
-                pos = lo;
-                rank[e] += pos;
-            }
-        }
-#pragma unroll
-        for (int e = 0; e < MAXC; ++e)
-            if (x[e] != 0ull && rank[e] < k) sorted[rank[e]] = x[e];
-    }
-    __syncthreads();
-    const int total = (int) sc.count;
-    return total < k ? total : k;
-}
-
 // The one-warp part of the draw for at most 64 candidates: pj[j] = exp(v_j - v_0) and acc[j] = exp((v_j - v_0) / T)
 // are in shared memory, the uniform in sc.hist.  Lane 0 walks the running sums left to right, as the reference adds
 // (src/kernels.cu:702-719); every lane then holds candidates j = lane and lane + 32, and the three decisions (top-p
@@ -386,10 +313,11 @@ __device__ __forceinline__ void draw_warp(const uint64_t * sorted, int nk, doubl
 }
 
 // The tail of k_sample (src/kernels.cu:698-720) over the nk sorted candidates: candidate softmax, top-p / min-p
-// cut, temperature weights, Philox draw.  exp and the quotients are per-element and run in parallel; the three
-// running sums keep the reference's left-to-right order: `sum` then `cum` on thread 0, the weight prefix (which
-// is both wsum and the acc of the inverse-CDF walk) on thread 32.  qj aliases the selection staging (k_cap
-// doubles).  All NT threads; block synchronised on entry.  p.counter is the counter of this row.
+// cut, temperature weights, Philox draw.  exp and the quotients are per-element and run in parallel; for up to 64
+// candidates the three running sums keep the reference's left-to-right order (draw_warp: `sum` and the weight
+// prefix - which is both wsum and the acc of the inverse-CDF walk - side by side, then `cum`).  qj aliases the
+// selection staging (k_cap doubles).  All NT threads; block synchronised on entry.  p.counter is the counter of
+// this row.
 template <int NT>
 __device__ void draw_tail(const uint64_t * sorted, int nk, double * pj, double * acc, double * qj, SelectScratch & sc,
                           const fns_b200_params & p, int k_cap, int32_t * out_token, fns_b200_cand * out_cands) {
