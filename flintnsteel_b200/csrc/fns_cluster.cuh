@@ -34,8 +34,66 @@ struct ClusterShared {
     uint64_t hbar;                // ... and of the history ids' 
     uint32_t region_n[kClusterCtas];  // CTA 0: how many candidates every CTA sent
     uint32_t bound_word;          // order word of the bound (0: none)
-    __align__(16) uint32_t wit[kClusterCtas * 16];  // CTA 0: the witnesses, two per warp of the cluster
+    uint32_t local_bound[kClusterCtas];  // second chance: the bound that each CTA could make of its own threads' maxima
+    __align__(16) uint32_t wit[kClusterCtas * 16];  // the witnesses, two per warp of the cluster (every CTA gets a copy)
 };
+
+// The k-th largest of 256 order words in shared memory (0 = no value; words below 0x00800000 stand for no finite
+// element), for one warp: every lane takes eight words, the bits in which the words differ are found first, and the
+// search decides up to 14 bits from the highest of them downwards, two bits per step with three warp-wide counts that
+// do not wait for one another; it stops early once at most four words too many remain.  Returns a word that at least
+// k of them reach (not always the largest such), or 0 when there are fewer than k.  The same value in every lane.
+__device__ __forceinline__ uint32_t warp_kth_of_256(const uint32_t * w256, int k) {
+    const int lane = threadIdx.x & 31;
+    uint32_t w8[8];
+    {
+        const uint4 lo4 = *reinterpret_cast<const uint4 *>(&w256[lane * 8]), hi4 = *reinterpret_cast<const uint4 *>(&w256[lane * 8 + 4]);
+        w8[0] = lo4.x; w8[1] = lo4.y; w8[2] = lo4.z; w8[3] = lo4.w;
+        w8[4] = hi4.x; w8[5] = hi4.y; w8[6] = hi4.z; w8[7] = hi4.w;
+    }
+    uint32_t wo = 0u, wa = 0xffffffffu, have = 0u;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        if (w8[q] < 0x00800000u) w8[q] = 0u;  // (no finite element behind it)
+        else {
+            wo |= w8[q];
+            wa &= w8[q];
+            ++have;
+        }
+    }
+    wo = __reduce_or_sync(kFull, wo);
+    wa = __reduce_and_sync(kFull, wa);
+    have = __reduce_add_sync(kFull, have);
+    uint32_t bw = 0u;
+    if (have >= (uint32_t) k) {  // else: fewer than k words, no bound
+        const uint32_t varying = wo & ~wa;
+        bw = varying ? (wa & ~((2u << (31 - __clz((int) varying))) - 1u)) : wa;  // the common prefix: a valid bound
+        if (varying) {
+            const int top = 31 - __clz((int) varying);
+            const int stop = top > 13 ? top - 13 : 0;
+#pragma unroll 1
+            for (int bit = top; bit >= stop; bit -= 2) {
+                const uint32_t b1 = 1u << bit, b0 = bit > stop ? 1u << (bit - 1) : 0u;
+                uint32_t c1 = 0u, c10 = 0u, c0 = 0u;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    c1 += w8[q] >= (bw | b1) ? 1u : 0u;
+                    c10 += w8[q] >= (bw | b1 | b0) ? 1u : 0u;
+                    c0 += w8[q] >= (bw | b0) ? 1u : 0u;
+                }
+                c1 = __reduce_add_sync(kFull, c1);
+                c10 = __reduce_add_sync(kFull, c10);
+                c0 = __reduce_add_sync(kFull, c0);
+                uint32_t tot = 0xffffffffu;
+                if (c10 >= (uint32_t) k) bw |= b1 | b0, tot = c10;
+                else if (c1 >= (uint32_t) k) bw |= b1, tot = c1;
+                else if (c0 >= (uint32_t) k) bw |= b0, tot = c0;
+                if (tot <= (uint32_t) k + 4u) break;  // close enough: at most four words too many
+            }
+        }
+    }
+    return bw >= 0x00800000u ? bw : 0u;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs a) {
@@ -264,60 +322,31 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
     }
     cluster.sync();
 
-    // 4. the bound: the k-th largest witness.  One warp does it without a block barrier: every lane takes eight
-    // witnesses, the bits in which the witnesses differ are found first, and the search decides up to 14 bits from the
-    // highest of them downwards with one warp-wide count per bit.
+    // 4. the bound: the k-th largest witness, found by one warp of every CTA in its own copy of the witnesses.
     if (warp == 0) {
-        uint32_t w8[8];
-        {
-            const uint4 lo4 = *reinterpret_cast<const uint4 *>(&cs.wit[lane * 8]), hi4 = *reinterpret_cast<const uint4 *>(&cs.wit[lane * 8 + 4]);
-            w8[0] = lo4.x; w8[1] = lo4.y; w8[2] = lo4.z; w8[3] = lo4.w;
-            w8[4] = hi4.x; w8[5] = hi4.y; w8[6] = hi4.z; w8[7] = hi4.w;
-        }
-        uint32_t wo = 0u, wa = 0xffffffffu, have = 0u;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            if (w8[q] < 0x00800000u) w8[q] = 0u;  // (no finite element behind it)
-            else {
-                wo |= w8[q];
-                wa &= w8[q];
-                ++have;
-            }
-        }
-        wo = __reduce_or_sync(kFull, wo);
-        wa = __reduce_and_sync(kFull, wa);
-        have = __reduce_add_sync(kFull, have);
-        uint32_t bw = 0u;
-        if (have >= (uint32_t) k) {  // else: fewer than k witnesses, no bound
-            const uint32_t varying = wo & ~wa;
-            bw = varying ? (wa & ~((2u << (31 - __clz((int) varying))) - 1u)) : wa;  // the common prefix: a valid bound
-            if (varying) {
-                const int top = 31 - __clz((int) varying);
-                const int stop = top > 13 ? top - 13 : 0;
-#pragma unroll 1
-                for (int bit = top; bit >= stop; bit -= 2) {  // two bits per step: three counts that do not wait for one another
-                    const uint32_t b1 = 1u << bit, b0 = bit > stop ? 1u << (bit - 1) : 0u;
-                    uint32_t c1 = 0u, c10 = 0u, c0 = 0u;
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        c1 += w8[q] >= (bw | b1) ? 1u : 0u;
-                        c10 += w8[q] >= (bw | b1 | b0) ? 1u : 0u;
-                        c0 += w8[q] >= (bw | b0) ? 1u : 0u;
-                    }
-                    c1 = __reduce_add_sync(kFull, c1);
-                    c10 = __reduce_add_sync(kFull, c10);
-                    c0 = __reduce_add_sync(kFull, c0);
-                    uint32_t tot = 0xffffffffu;
-                    if (c10 >= (uint32_t) k) bw |= b1 | b0, tot = c10;
-                    else if (c1 >= (uint32_t) k) bw |= b1, tot = c1;
-                    else if (c0 >= (uint32_t) k) bw |= b0, tot = c0;
-                    if (tot <= (uint32_t) k + 4u) break;  // close enough: at most four witnesses too many
-                }
-            }
-        }
-        if (lane == 0) cs.bound_word = bw >= 0x00800000u ? bw : 0u;
+        const uint32_t bw = warp_kth_of_256(cs.wit, k);
+        if (lane == 0) cs.bound_word = bw;
     }
     __syncthreads();
+    if (cs.bound_word == 0u) {  // (the same in every CTA: all searched the same witnesses)
+        // Fewer than k witnesses.  Under a mask whose allowed ids lie in a few slices that is no proof that the row has
+        // fewer than k candidates: a CTA whose own threads hold k maxima makes a bound of them, every CTA gets every
+        // such bound, and the largest is the row's.  (Two warps' witnesses per CTA were all that it could send above.)
+        uint32_t * w256 = reinterpret_cast<uint32_t *>(lbuf);  // (the CTA's buffer is not in use yet)
+        w256[tid] = tmax > -INFINITY ? order_word(tmax) : 0u;
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t mine = warp_kth_of_256(w256, k);
+            if (lane < kClusterCtas) cluster.map_shared_rank(&cs, lane)->local_bound[rank] = mine;
+        }
+        cluster.sync();
+        uint32_t best = 0u;
+#pragma unroll
+        for (int r = 0; r < kClusterCtas; ++r) best = max(best, cs.local_bound[r]);
+        __syncthreads();  // (w256 is the candidate buffer again)
+        if (tid == 0) cs.bound_word = best;
+        __syncthreads();
+    }
     float thr_v = cs.bound_word ? word_value(cs.bound_word) + 0.0f : -FLT_MAX;
     uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
     auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add

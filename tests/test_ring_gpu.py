@@ -173,16 +173,17 @@ def test_few_rows_with_equal_values_and_hot_histories(dev, oracle):
 
 
 def test_few_rows_under_masks_that_leave_no_bound(dev, oracle):
-    """A mask that allows a few hundred ids, all in one or two slices: too few witnesses for a bound, so every allowed
-    id is a candidate, and the CTA that holds them all sends only its own best k."""
+    """A mask that allows a few dozen to a few thousand ids, all in one or two slices: too few witnesses for a bound.
+    With fewer than k allowed ids every one is a candidate and the CTA that holds them sends only its own best k; with
+    more, the CTA's own thread maxima give the row its bound."""
     n = 151_936
     g = wl.rng(123)
-    rows = 10
+    rows = 12
     x = wl.gaussian_logits(g, rows, n, 2.5)
     masks = np.zeros((rows, (n + 31) // 32), np.uint32)
     for r in range(rows):
         start = int(g.integers(0, n - 4000))
-        ids = start + np.sort(g.choice(3000, size=(30, 130, 200, 600, 1500)[r % 5], replace=False))
+        ids = start + np.sort(g.choice(3000, size=(30, 130, 200, 600, 1500, 2600)[r % 6], replace=False))
         np.bitwise_or.at(masks[r], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
     hist = g.integers(0, n, size=(rows, 256), dtype=np.int32)
     p = make_params(rows, temperature=0.8, top_k=64, top_p=0.97, repetition=1.1, presence=0.2, frequency=0.1, seed=9)
