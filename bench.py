@@ -468,6 +468,33 @@ def batch1_latency(torch, dev, local):
     res["sessions8_masked_penalised"] = {"us_per_call_graph": a.elapsed_time(b) * 1e3 / (40 * 50), "rows": 8,
                                          "plan": s.plan(0, w.vocab, 8, w.history.shape[1])}
     s.close()
+    # one session through the engine glue, as the reference's decode loop uses Engine::pick: logits on the GPU, the
+    # grammar mask from host memory, the history on the device, the token back on the host - wall clock per token
+    import time
+
+    from flintnsteel_b200.sampler import Engine
+    w = wl.grammar_row()
+    eng = Engine(local, max_rows=1, vocab=w.vocab, k_cap=64, max_history=4096)
+    lg = torch.from_numpy(w.logits).to(dev)
+    pr = w.params.copy()
+
+    def token_step(i):
+        pr["counter"] = i
+        eng.pick_async(lg, pr, masks_host=w.masks)
+        eng.append(eng.device_tokens_ptr(), 1, 1)
+        return eng.pick_wait(1)
+
+    for i in range(200):
+        token_step(i)
+    eng.reset()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(2000):
+        token_step(i)
+    res["engine_one_session_step"] = {"us_per_token_wall": (time.perf_counter() - t0) / 2000 * 1e6,
+                                      "note": "pick_async + append + pick_wait from this Python process (three ctypes "
+                                              "calls per token); the kernel's share is the grammar row's figure above"}
+    eng.close()
     # config 3: one verification window (3 draft positions + bonus = 4 rows), greedy, accept length on the device
     sw = wl.spec_windows(seed=1, windows=1, n_draft=3)
     s = Sampler(local, max_rows=4, max_vocab=sw.vocab, k_cap=64, max_history=0)

@@ -56,6 +56,7 @@ struct Slot {
     int32_t * draft_d;
     int32_t * accept_d;
     int32_t * mask_rows_d;
+    int32_t * tokens_hd;  // tokens_h as the GPU addresses it (NULL until first asked for, or if it cannot)
     void * logits_d;      // staging for logits that arrive in host memory: one per slot, since the kernel of the older
     size_t logits_bytes;  // pick may still read its copy; grows on first use (cudaFree waits for the device once)
     cudaEvent_t done;
@@ -269,20 +270,33 @@ int fns_b200_engine_pick_async(fns_b200_engine * e, const void * logits, int log
         hist_len_d = e->sess_history_len;
         hstride = e->max_history;
     }
-    if ((err = bring(s.params_h, s.params_d, params_host, (size_t) rows, stable, st)) != cudaSuccess)
-        return ecuda(e, err, "params copy");
+    // One session (the reference's own shape, src/engine.cu:823-852): the parameters travel as a kernel argument and
+    // the kernel writes the token straight into the slot's page-locked host word (which the GPU addresses too), so the
+    // step costs the mask upload, one launch and the event - no copy of parameters in, no copy of the token out.
+    if (rows == 1 && !s.tokens_hd) s.tokens_hd = static_cast<int32_t *>(const_cast<void *>(device_view(s.tokens_h)));
+    int32_t * token_word = rows == 1 ? s.tokens_hd : nullptr;
     fns_b200_hint_host_logits(e->sampler, in_place != nullptr);
-    const int rc = fns_b200_sample_rows(e->sampler, lg, dtype, row_stride, e->vocab, rows, masks_host ? s.masks_d : nullptr,
-                                        e->words, hist_d, hstride, hist_len_d, s.params_d, s.tokens_d, st);
+    int rc;
+    if (token_word) {
+        rc = fns_b200_sample_one_with_history(e->sampler, lg, dtype, e->vocab, masks_host ? s.masks_d : nullptr, hist_d, hstride,
+                                              hist_len_d, params_host, token_word, st);
+    } else {
+        if ((err = bring(s.params_h, s.params_d, params_host, (size_t) rows, stable, st)) != cudaSuccess) {
+            fns_b200_hint_host_logits(e->sampler, 0);
+            return ecuda(e, err, "params copy");
+        }
+        rc = fns_b200_sample_rows(e->sampler, lg, dtype, row_stride, e->vocab, rows, masks_host ? s.masks_d : nullptr, e->words,
+                                  hist_d, hstride, hist_len_d, s.params_d, s.tokens_d, st);
+    }
     fns_b200_hint_host_logits(e->sampler, 0);
     if (rc != FNS_B200_OK) return esampler(e, rc);
-    if ((err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) !=
-            cudaSuccess ||
+    if ((!token_word &&
+         (err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) != cudaSuccess) ||
         (err = cudaEventRecord(s.done, st)) != cudaSuccess)
         return ecuda(e, err, "token copy");
     s.rows = rows;
     s.busy = true;
-    e->last_tokens = s.tokens_d;
+    e->last_tokens = token_word ? token_word : s.tokens_d;
     e->head = (e->head + 1) % kSlots;
     return FNS_B200_OK;
 }

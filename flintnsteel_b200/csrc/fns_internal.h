@@ -24,6 +24,13 @@ int fns_b200_set_threads(fns_b200_sampler * s, int threads);
 /* Calls of up to `rows` rows take the cluster kernel (0: never).  For the same tests. */
 int fns_b200_set_cluster_rows(fns_b200_sampler * s, int rows);
 
+/* One row with its parameters passed by value from the host (as fns_b200_sample_one) and a history in device memory
+ * (history [history_stride] ids, history_len [1]): the engine glue's one-session step, which then uploads nothing
+ * but the mask. */
+int fns_b200_sample_one_with_history(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
+                                     const int32_t * history, int64_t history_stride, const int32_t * history_len,
+                                     const fns_b200_params * params_host, int32_t * out_token, void * stream);
+
 /* The engine glue says that the logits of the handle's next calls lie in page-locked HOST memory (on = 1) or in
  * device memory (on = 0): host logits are read in place by the kernel that skips every vector the mask excludes,
  * never by the bulk-copy kernel, which would move whole chunks over PCIe. */

@@ -2104,6 +2104,17 @@ int fns_b200_sample_one(fns_b200_sampler * s, const void * logits, int dtype, in
     return rc;
 }
 
+int fns_b200_sample_one_with_history(fns_b200_sampler * s, const void * logits, int dtype, int vocab, const uint32_t * mask,
+                                     const int32_t * history, int64_t history_stride, const int32_t * history_len,
+                                     const fns_b200_params * params_host, int32_t * out_token, void * stream) {
+    if (!s) return FNS_B200_ERR_ARG;
+    if (!out_token || !params_host) return fail(s, FNS_B200_ERR_ARG, "out_token or params_host null");
+    DeviceGuard g(s->device);
+    Plan pl;
+    return run_select(s, logits, dtype, vocab, vocab, 1, 0, mask, (vocab + 31) / 32, nullptr, history, history_stride, history_len,
+                      nullptr, 0, nullptr, params_host, out_token, nullptr, (cudaStream_t) stream, pl);
+}
+
 int fns_b200_select_rows(fns_b200_sampler * s, const void * logits, int dtype, int64_t row_stride, int vocab, int rows,
                          int32_t id_base, const uint32_t * masks, int64_t mask_stride_words,
                          const int32_t * history, int64_t history_stride, const int32_t * history_len,
