@@ -41,6 +41,9 @@ def test_ragged_vocabularies_masked_and_unmasked(dev, oracle, n, bf16):
     w2 = wl.Workload("ragged_unmasked", logits, p, None, hist, hl, bf16=bf16, k_cap=64)
     check_against_oracle(oracle, w2, *run_rows(w2, dev, max_history=64, cluster_rows=0))   # k_ring
     check_against_oracle(oracle, w2, *run_rows(w2, dev, max_history=64, cluster_rows=6))   # six clusters
+    w3 = wl.Workload("ragged_masked_k64", logits, p, masks, hist, hl, bf16=bf16, k_cap=64)
+    check_against_oracle(oracle, w3, *run_rows(w3, dev, max_history=64, cluster_rows=6))   # six clusters, under the masks
+    check_against_oracle(oracle, w3, *run_rows(w3, dev, max_history=64, cluster_rows=0))   # k_select
 
 
 def test_equal_values_take_the_careful_walk(dev, oracle):
