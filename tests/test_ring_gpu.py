@@ -186,7 +186,10 @@ def test_few_rows_under_masks_that_leave_no_bound(dev, oracle):
     masks = np.zeros((rows, (n + 31) // 32), np.uint32)
     for r in range(rows):
         start = int(g.integers(0, n - 4000))
-        ids = start + np.sort(g.choice(3000, size=(30, 130, 200, 600, 1500, 2600)[r % 6], replace=False))
+        if r >= 9:  # one contiguous block: few threads see an allowed id at all (150 ids: 38 threads, fewer than k)
+            ids = start + np.arange((150, 200, 400)[r - 9])
+        else:
+            ids = start + np.sort(g.choice(3000, size=(30, 130, 200, 600, 1500, 2600)[r % 6], replace=False))
         np.bitwise_or.at(masks[r], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
     hist = g.integers(0, n, size=(rows, 256), dtype=np.int32)
     p = make_params(rows, temperature=0.8, top_k=64, top_p=0.97, repetition=1.1, presence=0.2, frequency=0.1, seed=9)
