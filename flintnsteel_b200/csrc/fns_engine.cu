@@ -427,20 +427,32 @@ int fns_b200_engine_pick_async_dl(fns_b200_engine * e, const void * logits, int 
         e->slot_used[slot] = e->tick;
         s.mask_rows_h[r] = slot;
     }
-    if ((err = cudaMemcpyAsync(s.mask_rows_d, s.mask_rows_h, (size_t) rows * sizeof(int32_t), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-        (err = stage(s.params_h, s.params_d, params_host, (size_t) rows, st)) != cudaSuccess)
-        return ecuda(e, err, "mask rows / params copy");
     const bool hist = e->max_history > 0;
-    const int rc = fns_b200_sample_rows_shared_masks(e->sampler, logits, dtype, row_stride, e->vocab, rows, e->cache_d, e->words,
-                                                     s.mask_rows_d, hist ? e->sess_history : nullptr, hist ? e->max_history : 0,
-                                                     hist ? e->sess_history_len : nullptr, s.params_d, s.tokens_d, st);
+    // one session (see fns_b200_engine_pick_async): the mask is its cache slot, the parameters a kernel argument, the
+    // token goes straight into the slot's page-locked host word - a state that the cache holds costs a launch and an event
+    if (rows == 1 && !s.tokens_hd) s.tokens_hd = static_cast<int32_t *>(const_cast<void *>(device_view(s.tokens_h)));
+    int32_t * token_word = rows == 1 ? s.tokens_hd : nullptr;
+    int rc;
+    if (token_word) {
+        const uint32_t * one_mask = mask_states_host[0] == FNS_B200_NO_MASK ? nullptr : e->cache_d + (size_t) s.mask_rows_h[0] * e->words;
+        rc = fns_b200_sample_one_with_history(e->sampler, logits, dtype, e->vocab, one_mask, hist ? e->sess_history : nullptr,
+                                              hist ? e->max_history : 0, hist ? e->sess_history_len : nullptr, params_host, token_word, st);
+    } else {
+        if ((err = cudaMemcpyAsync(s.mask_rows_d, s.mask_rows_h, (size_t) rows * sizeof(int32_t), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+            (err = stage(s.params_h, s.params_d, params_host, (size_t) rows, st)) != cudaSuccess)
+            return ecuda(e, err, "mask rows / params copy");
+        rc = fns_b200_sample_rows_shared_masks(e->sampler, logits, dtype, row_stride, e->vocab, rows, e->cache_d, e->words, s.mask_rows_d,
+                                               hist ? e->sess_history : nullptr, hist ? e->max_history : 0,
+                                               hist ? e->sess_history_len : nullptr, s.params_d, s.tokens_d, st);
+    }
     if (rc != FNS_B200_OK) return esampler(e, rc);
-    if ((err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) != cudaSuccess ||
+    if ((!token_word &&
+         (err = cudaMemcpyAsync(s.tokens_h, s.tokens_d, (size_t) rows * sizeof(int32_t), cudaMemcpyDeviceToHost, st)) != cudaSuccess) ||
         (err = cudaEventRecord(s.done, st)) != cudaSuccess)
         return ecuda(e, err, "token copy");
     s.rows = rows;
     s.busy = true;
-    e->last_tokens = s.tokens_d;
+    e->last_tokens = token_word ? token_word : s.tokens_d;
     e->head = (e->head + 1) % kSlots;
     return FNS_B200_OK;
 }

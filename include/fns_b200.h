@@ -263,8 +263,10 @@ int fns_b200_engine_pick_async_dl(fns_b200_engine * e, const void * logits, int 
 int fns_b200_engine_words(const fns_b200_engine * e);
 /* Engine::pick_wait (src/engine.cu:849-852): waits for the oldest pick in flight; tokens_host[rows]. */
 int fns_b200_engine_pick_wait(fns_b200_engine * e, int32_t * tokens_host);
-/* Device copy of the tokens of the latest pick (the reference's io_ + 2), for a forward pass that is queued
- * before the host has seen the token (Engine::step_next, src/engine.cu:796-800). */
+/* The tokens of the latest pick where the GPU can read them (the reference's io_ + 2), for a forward pass that is
+ * queued before the host has seen the token (Engine::step_next, src/engine.cu:796-800).  After a pick of one row this
+ * is a page-locked host word that the GPU addresses (the kernel writes the token there and nothing is copied back);
+ * after a pick of several rows it is device memory. */
 const int32_t * fns_b200_engine_device_tokens(const fns_b200_engine * e);
 /* Engine::reset_presence (src/engine.cu:854-860): forgets the device-side history of every session. */
 int fns_b200_engine_reset(fns_b200_engine * e, void * stream);

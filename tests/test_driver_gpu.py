@@ -94,6 +94,36 @@ def test_bitmask_tensor_and_state_cache(dev, oracle):
     eng.close()
 
 
+def test_one_session_with_cached_grammar_states(dev, oracle):
+    """The decode loop's own shape: one row per call, the mask named by its grammar state, the history kept on the
+    device.  A state that the cache holds uploads nothing; the tokens are the oracle's with the history so far."""
+    w = wl.session_batch(seed=62, rows=4, vocab=50_000, history=8)
+    eng = Engine(0, max_rows=1, vocab=w.vocab, k_cap=64, max_history=64)
+    eng.mask_cache(3)
+    lg = torch.from_numpy(w.logits).to(dev)
+    p = w.params[:1].copy()
+    p["temperature"], p["repetition"], p["presence"], p["frequency"] = 0.7, 1.2, 0.3, 0.2
+    hist: list[int] = []
+    states = [5, 6, 5, 5, 0xFFFFFFFFFFFFFFFF, 6, 7, 8, 5, 6]   # (three slots: 8 pushes 5 out, the last 5 pushes 6 out)
+    for step, st in enumerate(states):
+        r = step % 4
+        masked = st != 0xFFFFFFFFFFFFFFFF
+        m = w.masks[(st - 5) % 4][None, :] if masked else None
+        p["counter"] = step
+        eng.pick_async_dl(lg[r:r + 1], p, masks=None if m is None else torch.from_numpy(m.view(np.int32).copy()),
+                          mask_states=np.array([st], np.uint64))
+        eng.append(eng.device_tokens_ptr(), 1, 1)
+        tok = int(eng.pick_wait(1)[0])
+        h = np.array(hist + [0] * (64 - len(hist)), np.int32)[None, :]
+        want, _ = oracle.sample_rows(w.logits[r:r + 1], p, 64, m, h, np.array([len(hist)], np.int32))
+        assert tok == want[0], (step, tok, want)
+        if tok >= 0:
+            hist.append(tok)
+    hits, misses, _ = eng.mask_stats()
+    assert misses == 6 and hits == 3   # 5, 6, 7, 8 and then 5 and 6 again are uploaded; three calls find theirs
+    eng.close()
+
+
 class ToyModel:
     """Logits that depend on the last token only (a table of rows on the device): greedy decoding soon cycles, so the
     prompt-lookup draft finds continuations; sampling leaves the cycle now and then."""
