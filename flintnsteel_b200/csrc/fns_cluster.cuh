@@ -27,6 +27,7 @@ constexpr int kClusterRegion = 128;   // keys a CTA may send to CTA 0 directly; 
 constexpr int kClusterBuf = kClusterCtas * kClusterRegion;
 constexpr int kClusterLocal = 2048;   // keys of a CTA's own buffer (careful way; in CTA 0 also the regions side by side)
 constexpr int kClusterMaxK = 128;     // 256 witnesses give a bound for k up to this
+constexpr int kClusterRankMax = 640;  // CTA 0 ranks up to this many keys by counting (n * n / 256 compares per thread)
 
 struct ClusterShared {
     SelectShared s;
@@ -500,9 +501,11 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
         // every CTA has its own region of CTA 0's buffer: plain remote stores, no reservation, no round trip
         uint32_t n_loc = sh.n_cand;
         const uint64_t * src = lbuf;
-        if (n_loc > (uint32_t) kClusterRegion && n_loc <= (uint32_t) kClusterLocal) {
+        const bool no_bound = cs.bound_word == 0u;  // then every allowed id of the row is a candidate
+        if ((n_loc > (uint32_t) kClusterRegion || (no_bound && n_loc > (uint32_t) k)) && n_loc <= (uint32_t) kClusterLocal) {
             // More than a region holds, but all of it is here (a sparse mask leaves too few witnesses for a bound, and
-            // its allowed ids may all lie in one slice): only this CTA's best k can matter, and k fits a region.
+            // its allowed ids may all lie in one slice): only this CTA's best k can matter, and k fits a region.  Without
+            // a bound the same cut is made as soon as the CTA has more than k, so that CTA 0 has less to rank.
             int got;
             if (n_loc <= (uint32_t) kRankSelectMax) {
                 got = block_rank_select<NT>(lbuf, (int) n_loc, k, lsel);
@@ -599,7 +602,7 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
                 for (int j = tid; j < a.k_cap; j += NT) sorted[j] = 0ull;
                 __syncthreads();
             }
-            if (n <= kRankSelectMax) {
+            if (n <= kClusterRankMax) {
                 nk = block_rank_select<NT>(lbuf, n, k, sorted);
             } else {
                 const uint64_t tau = block_kth_key<NT>(lbuf, n, k, sh.sc);
