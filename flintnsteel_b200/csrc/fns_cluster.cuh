@@ -348,6 +348,7 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
         if (tid == 0) cs.bound_word = best;
         __syncthreads();
     }
+    const bool no_bound = cs.bound_word == 0u;  // (the same in every CTA of the cluster)
     float thr_v = cs.bound_word ? word_value(cs.bound_word) + 0.0f : -FLT_MAX;
     uint64_t thr_key = (uint64_t) order_word(thr_v) << 32;
     auto penalised = [&](float v, float cnt) -> float {  // each step rounded on its own: no fused multiply-add
@@ -501,24 +502,38 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
         // every CTA has its own region of CTA 0's buffer: plain remote stores, no reservation, no round trip
         uint32_t n_loc = sh.n_cand;
         const uint64_t * src = lbuf;
-        const bool no_bound = cs.bound_word == 0u;  // then every allowed id of the row is a candidate
-        if ((n_loc > (uint32_t) kClusterRegion || (no_bound && n_loc > (uint32_t) k)) && n_loc <= (uint32_t) kClusterLocal) {
-            // More than a region holds, but all of it is here (a sparse mask leaves too few witnesses for a bound, and
-            // its allowed ids may all lie in one slice): only this CTA's best k can matter, and k fits a region.  Without
-            // a bound the same cut is made as soon as the CTA has more than k, so that CTA 0 has less to rank.
+        if (no_bound && n_loc <= (uint32_t) kClusterLocal) {
+            // No bound (a sparse mask left too few witnesses, and no CTA had k maxima of its own): every allowed id of
+            // the row is a candidate.  Every CTA sends its own best k, sorted, at a distance of k: CTA 0 ranks their
+            // union as it comes while that is small, and merges sixteen sorted lists when it is not.
+            uint64_t * dst = gbuf0 + (size_t) rank * k;
             int got;
             if (n_loc <= (uint32_t) kRankSelectMax) {
-                got = block_rank_select<NT>(lbuf, (int) n_loc, k, lsel);
+                got = block_rank_select<NT>(lbuf, (int) n_loc, k, dst);
             } else {
                 const uint64_t tau = block_kth_key<NT>(lbuf, (int) n_loc, k, sh.sc);
                 got = block_take<NT>(lbuf, (int) n_loc, k, tau, lsel, sh.sc);
+                block_rank_sort<NT>(lsel, got, dst);
             }
-            __syncthreads();
-            n_loc = (uint32_t) got;
-            src = lsel;
+            for (int j = got + tid; j < k; j += NT) dst[j] = 0ull;
+            if (tid == 0) cs0->region_n[rank] = (uint32_t) got;
+        } else {
+            if (n_loc > (uint32_t) kClusterRegion && n_loc <= (uint32_t) kClusterLocal) {
+                // More than a region holds, but all of it is here: only this CTA's best k can matter, and k fits a region.
+                int got;
+                if (n_loc <= (uint32_t) kRankSelectMax) {
+                    got = block_rank_select<NT>(lbuf, (int) n_loc, k, lsel);
+                } else {
+                    const uint64_t tau = block_kth_key<NT>(lbuf, (int) n_loc, k, sh.sc);
+                    got = block_take<NT>(lbuf, (int) n_loc, k, tau, lsel, sh.sc);
+                }
+                __syncthreads();
+                n_loc = (uint32_t) got;
+                src = lsel;
+            }
+            if (tid == 0) cs0->region_n[rank] = n_loc;  // (still more than a region holds: the careful way follows)
+            for (uint32_t i = tid; i < n_loc && i < (uint32_t) kClusterRegion; i += NT) gbuf0[(size_t) rank * kClusterRegion + i] = src[i];
         }
-        if (tid == 0) cs0->region_n[rank] = n_loc;  // (still more than a region holds: the careful way follows)
-        for (uint32_t i = tid; i < n_loc && i < (uint32_t) kClusterRegion; i += NT) gbuf0[(size_t) rank * kClusterRegion + i] = src[i];
         __syncthreads();
         if (tid == 0) sh.n_cand = 0u;  // (the careful way starts from an empty buffer)
     }
@@ -588,7 +603,7 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
         int32_t * tok = a.out_tokens ? a.out_tokens + row : nullptr;
         fns_b200_cand * oc = a.out_cands ? a.out_cands + (size_t) row * a.k_cap : nullptr;
         int nk;
-        if (careful) {
+        if (careful || (no_bound && n_glob > (uint32_t) kClusterRankMax)) {  // sixteen sorted lists of k
             nk = merge_lists<NT>(gbuf, kClusterCtas, k, gsel, sorted, reinterpret_cast<uint64_t *>(pj), 2 * a.k_cap, sh.sc, k, a.k_cap);
         } else {
             // the regions side by side in the CTA's own buffer (sixteen threads per region), then the ordinary ranking
@@ -598,7 +613,8 @@ __global__ void __launch_bounds__(kClusterThreads, 1) k_cluster(const SelectArgs
                 uint32_t before = 0u;
                 for (int q = 0; q < r; ++q) before += cs.region_n[q];
                 const uint32_t cnt = cs.region_n[r];
-                for (uint32_t i = (uint32_t) (tid & 15); i < cnt; i += 16u) lbuf[before + i] = gbuf[(size_t) r * kClusterRegion + i];
+                const int apart = no_bound ? k : kClusterRegion;  // (without a bound the CTAs sent lists of k)
+                for (uint32_t i = (uint32_t) (tid & 15); i < cnt; i += 16u) lbuf[before + i] = gbuf[(size_t) r * apart + i];
                 for (int j = tid; j < a.k_cap; j += NT) sorted[j] = 0ull;
                 __syncthreads();
             }
